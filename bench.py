@@ -1,0 +1,299 @@
+"""MoE-layer benchmark: one step = prepare (device planning) + forward (dispatch GEMM with SwiGLU,
+combine GEMM, top-k reduce) of the expert-parallel layer on synthetic routing of a named workload.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference        # the reference layer math on the host cores (CPU arm)
+
+Prints ONE JSON line on rank 0.  `value` = whole-job TFLOP/s (6*H*I flops per routed copy) with
+inputs resident in HBM; `e2e` = the same through the public API with pinned host buffers copied
+in and the output copied out inside the timed region; `roofline` = the dispatch GEMM kernel
+against the measured HBM copy bandwidth; `cpu_baseline` = the CPU oracle layer on a bounded sample.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "moe_layer_tflops"
+UNIT = "TFLOP/s"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="qwen3-30b", choices=["qwen3-30b", "qwen3-235b", "k2"])
+    ap.add_argument("--strategy", default="overlap", choices=["overlap", "direct"])
+    ap.add_argument("--tokens", type=int, default=0, help="tokens per rank (default: the workload's)")
+    ap.add_argument("--cpu-baseline", type=int, default=1)
+    return ap.parse_args()
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return float(p["hbm_gbs"]), float(p.get("bf16_tflops", 1590.0)), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    Q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
+        "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def cpu_reference_sample(shape, ids, wts, seed, iters, tokens=128):
+    """The reference's fp32 SwiGLU layer (oracle/layer.py) on the first `tokens` tokens of rank 0, all host
+    threads.  Returns (TFLOP/s, seconds per pass, threads)."""
+    from oracle import layer as ol
+    from zepp_b200 import workloads as wl
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    T = min(tokens, ids.shape[1])
+    g = torch.Generator().manual_seed(777)
+    E = shape.num_experts
+    W1 = 0.02 * torch.randn(E, shape.ffn1, shape.hidden, generator=g)
+    W2 = 0.02 * torch.randn(E, shape.hidden, shape.ffn_hidden, generator=g)
+    x = wl.tokens(0, ids.shape[1], shape.hidden, seed=seed, dtype=torch.float32)[:T]
+    i0, w0 = ids[0, :T], wts[0, :T]
+    for _ in range(2):
+        ol.moe_reference_fp32(x, i0, w0, W1, W2)
+    ts = []
+    for _ in range(iters):
+        t0 = time.perf_counter()
+        ol.moe_reference_fp32(x, i0, w0, W1, W2)
+        ts.append(time.perf_counter() - t0)
+    sec = statistics.median(ts)
+    flops = 6.0 * shape.hidden * shape.ffn_hidden * T * shape.topk
+    return flops / sec / 1e12, sec, threads, T
+
+
+def run_reference(args, rank):
+    """CPU arm: the reference's layer math on the host cores, same metric/unit/config."""
+    if rank != 0:
+        return
+    from zepp_b200 import workloads as wl
+    shape, S, ids, wts, _, _ = wl.make(args.workload, max(args.gpus, 1), S=args.tokens or None)
+    for _ in range(max(args.warmup - 2, 0)):
+        pass
+    tf, sec, threads, T = cpu_reference_sample(shape, ids, wts, 0, max(args.steps, 3))
+    line = {"impl": "reference", "metric": METRIC, "value": tf, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: H={shape.hidden} I={shape.ffn_hidden} E={shape.num_experts} "
+                                   f"top-{shape.topk} SwiGLU, {S} tokens/rank", "sample": f"{T} tokens of rank 0 per step"},
+            "cpu_baseline": {"value": tf, "unit": UNIT, "cores": threads, "kind": "port",
+                             "sample": f"{T} tokens x top-{shape.topk}, fp32, all {shape.num_experts} experts resident"},
+            "e2e": {"value": tf, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    args = parse()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    import torch.distributed as dist
+    from zepp_b200 import EPMoE, EPMoEConfig
+    from zepp_b200 import workloads as wl
+    from zepp_b200.layer import LocalGroup
+
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE {world} (launch with torch.distributed.run)"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        group = dist.group.WORLD
+    else:
+        group = LocalGroup(0, 1)
+
+    shape, S, ids, wts, _, _ = wl.make(args.workload, world, S=args.tokens or None)
+    _, _, _, router_c, _ = wl.WORKLOADS[args.workload]
+    cfg = EPMoEConfig(shape=shape, ranks=world, ranks_per_node=world, max_tokens_per_rank=S,
+                      comm_strategy=args.strategy, swap=False, router_c=router_c)
+    layer = EPMoE(cfg, group, sizing_routing=ids, pool_routing=ids)
+    nlp = cfg.slots_per_rank
+    hosted = [int(e) for e in layer.placement.p2l[rank * nlp:(rank + 1) * nlp].tolist() if e >= 0]
+    wts_dev = wl.fast_weights(shape, hosted, dev)
+    layer.load_weights(lambda e: wts_dev[e][0], lambda e: wts_dev[e][1])
+    del wts_dev
+    ids_own = ids[rank].contiguous()
+    w_own = wts[rank].contiguous()
+    ids_d, w_d = ids_own.to(dev), w_own.to(dev)
+    n_x = 4
+    xs_host = [wl.tokens(rank, S, shape.hidden, seed=s).pin_memory() for s in range(n_x)]
+    xs_dev = [x.to(dev) for x in xs_host]
+    ids_pin, w_pin = ids_own.pin_memory(), w_own.pin_memory()
+    y_pin = torch.empty(S, shape.hidden, dtype=torch.bfloat16).pin_memory()
+    layer.prime(ids_d, w_d)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
+
+    def step_resident(i, marks=None):
+        plan = layer.prepare(ids_d, w_d, marks) if marks else layer.prepare(ids_d, w_d)
+        return layer.forward(xs_dev[i % n_x], plan, marks) if marks else layer.forward(xs_dev[i % n_x], plan)
+
+    ids_in = torch.empty_like(ids_d)
+    w_in = torch.empty_like(w_d)
+    x_in = torch.empty_like(xs_dev[0])
+
+    def step_e2e(i):
+        ids_in.copy_(ids_pin, non_blocking=True)
+        w_in.copy_(w_pin, non_blocking=True)
+        x_in.copy_(xs_host[i % n_x], non_blocking=True)
+        y = layer.forward(x_in, layer.prepare(ids_in, w_in))
+        y_pin.copy_(y, non_blocking=True)
+
+    # ---- device-resident steps (value) + per-kernel brackets (roofline)
+    for i in range(args.warmup):
+        step_resident(i)
+    layer.check()
+    sampler = ClockSampler(local_rank)
+    names = ("start", "plan_comm", "place", "plan", "dispatch", "act", "combine")
+    evs = [{n: ev() for n in names} for _ in range(args.steps)]
+    launches0 = layer.gpu_launches
+    barrier()
+    sampler.start()
+    t_begin, t_end = ev(), ev()
+    t_begin.record()
+    for i in range(args.steps):
+        e = evs[i]
+        e["start"].record()
+        step_resident(i, lambda n, e=e: e[n].record())
+    t_end.record()
+    barrier()
+    clocks = sampler.stop()
+    launches = layer.gpu_launches - launches0
+    layer.check()
+    ms_total = max_over_ranks(t_begin.elapsed_time(t_end))
+    ms_step = ms_total / args.steps
+    gemm1_ms = statistics.mean(e["plan"].elapsed_time(e["dispatch"]) for e in evs)
+    plan_ms = statistics.mean(e["start"].elapsed_time(e["plan"]) for e in evs)
+    comb_ms = statistics.mean(e["act"].elapsed_time(e["combine"]) for e in evs)
+
+    # ---- end-to-end steps through the public API with host buffers
+    for i in range(max(3, args.warmup // 2)):
+        step_e2e(i)
+    barrier()
+    t0, t1 = ev(), ev()
+    t0.record()
+    for i in range(args.steps):
+        step_e2e(i)
+    t1.record()
+    barrier()
+    ms_e2e = max_over_ranks(t0.elapsed_time(t1)) / args.steps
+    layer.check()
+
+    # ---- roofline of the dispatch GEMM kernel (HBM bound at these row counts)
+    H, I, K = shape.hidden, shape.ffn_hidden, shape.topk
+    splits, m_this = layer.tables("splits", "m_this")
+    gpe = cfg.groups_per_rank
+    mine = splits[rank * gpe:(rank + 1) * gpe].cpu()
+    active = int((mine > 0).sum())
+    m_r = int(m_this[0])
+    alg_bytes = 4.0 * H * I * active + 2.0 * H * m_r + 2.0 * I * m_r      # W1 of active experts + rows in + activations out
+    hbm_gbs, bf16_tf, peak_kind = peaks()
+    achieved = alg_bytes / (gemm1_ms * 1e-3) / 1e9
+    flops_step = 6.0 * H * I * S * K * world
+    value = flops_step / (ms_step * 1e-3) / 1e12
+    e2e_val = flops_step / (ms_e2e * 1e-3) / 1e12
+    t_flop = 6.0 * H * I * m_r / (bf16_tf * 1e12)
+    t_hbm = 6.0 * H * I * active / (hbm_gbs * 1e9)
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": f"{args.workload}: H={H} I={I} E={shape.num_experts} top-{K} SwiGLU, {S} tokens/rank, "
+                               f"{shape.num_experts // world} experts/rank, routing seed 0",
+                   "strategy": args.strategy, "parallelism": f"ep{world}", "router_c": router_c, "swap": 0,
+                   "l2": "expert weights streamed per step exceed the 126 MB L2 (inputs larger than L2)",
+                   "timed": "prepare (device planning) + forward"},
+        "latency_us": ms_step * 1e3,
+        "breakdown_us": {"plan": plan_ms * 1e3, "dispatch_gemm": gemm1_ms * 1e3, "combine_gemm_reduce": comb_ms * 1e3},
+        "roofline_layer": {"t_flop_us": t_flop * 1e6, "t_hbm_weights_us": t_hbm * 1e6,
+                           "frac_of_3term": max(t_flop, t_hbm) / (ms_step * 1e-3), "rows_this_rank": m_r},
+        "e2e": {"value": e2e_val, "unit": UNIT, "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": int(ids_pin.numel() * 4 + w_pin.numel() * 4 + xs_host[0].numel() * 2),
+                "d2h_bytes_per_step": int(y_pin.numel() * 2)},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "hbm", "kernel": "moe_gemm_kernel<gate|up + SwiGLU> (dispatch GEMM)", "achieved": achieved,
+                     "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs, "peak_kind": peak_kind,
+                     "traffic": None, "algorithmic_bytes": alg_bytes, "kernel_ms": gemm1_ms},
+        "clocks": clocks,
+    }
+    if rank == 0 and world == 1 and args.cpu_baseline:
+        tf, sec, threads, T = cpu_reference_sample(shape, ids, wts, 0, 10)
+        line["cpu_baseline"] = {"value": tf, "unit": UNIT, "cores": threads, "kind": "port", "ms_per_pass": sec * 1e3,
+                                "sample": f"{T} tokens x top-{K} of rank 0, fp32, oracle/layer.py on all host threads"}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    layer.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,192 @@
+"""The MoE layer through the public API (EPMoE over the C-ABI) against the CPU oracle: planner
+products bit-exact, outputs within rtol 2e-2 / atol 2e-2 (bf16 inputs, fp32 accumulation)."""
+import dataclasses
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import layer as ol
+from oracle import planner as op
+from zepp_b200 import EPMoE, EPMoEConfig, ModelShape
+from zepp_b200 import workloads as wl
+from zepp_b200.capacity import CapacityExceeded
+from zepp_b200.layer import LocalGroup, local_step, make_local_layers
+from zepp_b200.routing import Capacities
+
+pytestmark = pytest.mark.gpu
+RTOL = ATOL = 2e-2
+
+
+def _weights(shape):
+    W1 = torch.stack([wl.expert_w1(e, shape) for e in range(shape.num_experts)])
+    W2 = torch.stack([wl.expert_w2(e, shape) for e in range(shape.num_experts)])
+    return W1, W2
+
+
+def _reference(xs, ids, wts, W1, W2):
+    return [ol.moe_reference_fp32(xs[r], ids[r], wts[r], W1, W2) for r in range(len(xs))]
+
+
+def _close(y, ref, tag):
+    bad = ~torch.isclose(y.float().cpu(), ref, rtol=RTOL, atol=ATOL)
+    assert not bool(bad.any()), f"{tag}: {int(bad.sum())} of {bad.numel()} elements out of tolerance, " \
+                               f"max |err| {float((y.float().cpu() - ref).abs().max()):.4g}"
+
+
+def _run_local(shape, W, L, S, strategy, zipf=0.0, seed=0, steps=2, check_plan=True):
+    cfg = EPMoEConfig(shape=shape, ranks=W, ranks_per_node=L, max_tokens_per_rank=S, comm_strategy=strategy)
+    gen = torch.Generator().manual_seed(seed)
+    p = wl.popularity(shape.num_experts, zipf, gen)
+    ids, wts = wl.routing(W, S, shape.topk, p, gen)
+    layers, rts = make_local_layers(cfg, ids, ids, wait_limit_ms=500)
+    W1, W2 = _weights(shape)
+    for l in layers:
+        l.load_weights(lambda e: W1[e], lambda e: W2[e])
+    try:
+        for step in range(steps):
+            if step:
+                ids, wts = wl.routing(W, S, shape.topk, p, gen)
+            xs = [wl.tokens(r, S, shape.hidden, seed=seed + 10 * step) for r in range(W)]
+            ys = local_step(layers, [ids[r].cuda() for r in range(W)], [wts[r].cuda() for r in range(W)],
+                            [x.cuda() for x in xs])
+            for l in layers:
+                l.check()
+            refs = _reference(xs, ids, wts, W1, W2)
+            for r in range(W):
+                _close(ys[r], refs[r], f"{strategy} W{W} L{L} rank{r} step{step}")
+            if check_plan:
+                pl0 = layers[0].placement
+                pl = op.Placement(pl0.p2l.numpy(), pl0.l2p.numpy(), pl0.lcnts.numpy())
+                phys, _ = op.reference_route(ids.numpy(), pl, cfg.slots_per_rank, L, cfg.router_c)
+                vce = op.virtual_route(phys.reshape(W * S, -1), cfg.slots_per_rank, cfg.groups_per_rank)
+                splits, scat, sps, uc = op.routed_meta(vce, W, S, cfg.groups_per_rank, W // L, L)
+                for r, l in enumerate(layers):
+                    t = dict(zip(("vce", "splits", "scatter_index", "sps", "uc", "phys_own", "m_this"),
+                                 l.tables("vce", "splits", "scatter_index", "sps", "uc", "phys_own", "m_this")))
+                    assert np.array_equal(t["phys_own"].cpu().numpy().reshape(S, -1), phys[r]), (r, "phys")
+                    assert np.array_equal(t["vce"].cpu().numpy().reshape(vce.shape), vce), (r, "vce")
+                    assert np.array_equal(t["splits"].cpu().numpy(), splits), (r, "splits")
+                    assert np.array_equal(t["scatter_index"].cpu().numpy().reshape(scat.shape), scat), (r, "scatter")
+                    assert np.array_equal(t["sps"].cpu().numpy().reshape(sps.shape), sps), (r, "sps")
+                    assert np.array_equal(t["uc"].cpu().numpy().reshape(uc.shape), uc), (r, "uc")
+                    gpe = cfg.groups_per_rank
+                    assert int(t["m_this"][0]) == int(splits[r * gpe:(r + 1) * gpe].sum())
+    finally:
+        for l in layers:
+            l.close()
+        for rt in rts:
+            rt.destroy()
+
+
+SMALL = ModelShape(16, 4, 256, 128, act="swiglu")
+MID = ModelShape(32, 8, 512, 256, act="swiglu")
+
+
+@pytest.mark.parametrize("strategy", ["direct", "overlap"])
+def test_single_rank_small(strategy):
+    _run_local(SMALL, 1, 1, 32, strategy)
+
+
+@pytest.mark.parametrize("strategy", ["direct", "overlap"])
+def test_single_rank_many_rows_per_expert(strategy):
+    """More than one 128-row token tile per expert and ragged last tiles."""
+    _run_local(SMALL, 1, 1, 1000, strategy, zipf=1.0, steps=1)
+
+
+@pytest.mark.parametrize("strategy", ["direct", "overlap"])
+def test_single_rank_gelu(strategy):
+    shape = ModelShape(16, 4, 256, 128, act="gelu")
+    cfg = EPMoEConfig(shape=shape, ranks=1, ranks_per_node=1, max_tokens_per_rank=64, comm_strategy=strategy)
+    gen = torch.Generator().manual_seed(3)
+    ids, wts = wl.routing(1, 64, 4, wl.popularity(16, 0.0, gen), gen)
+    layer = EPMoE(cfg, LocalGroup(0, 1), ids, ids)
+    W1, W2 = _weights(shape)
+    layer.load_weights(lambda e: W1[e], lambda e: W2[e])
+    x = wl.tokens(0, 64, 256)
+    plan = layer.prepare(ids[0].cuda(), wts[0].cuda())
+    y = layer.forward(x.cuda(), plan)
+    layer.check()
+    ref = torch.zeros(64, 256)
+    for t in range(64):
+        for j in range(4):
+            e = int(ids[0, t, j])
+            h = torch.nn.functional.gelu(x[t].float() @ W1[e].float().t())
+            ref[t] += float(wts[0, t, j]) * (h @ W2[e].float().t())
+    _close(y, ref, f"gelu {strategy}")
+    layer.close()
+
+
+@pytest.mark.parametrize("strategy", ["direct", "overlap"])
+@pytest.mark.parametrize("W,L", [(2, 2), (4, 4), (8, 8)])
+def test_emulated_ranks_one_node(strategy, W, L):
+    _run_local(MID, W, L, 64, strategy, zipf=1.0 if W == 4 else 0.0)
+
+
+@pytest.mark.parametrize("W,L", [(4, 2), (8, 4), (8, 2)])
+def test_emulated_ranks_virtual_nodes(W, L):
+    """Replicated experts, capacity routing and the vacate pass (virtual nodes on one box)."""
+    _run_local(MID, W, L, 64, "overlap", zipf=1.0, seed=2)
+
+
+def test_fresh_payload_each_step_and_bitwise_repeat():
+    """A new x every step (a stale-delivery bug cannot pass, bench/replay.py:141-143) and identical
+    outputs when a step is repeated (deterministic combine)."""
+    shape, W, S = MID, 2, 64
+    cfg = EPMoEConfig(shape=shape, ranks=W, ranks_per_node=W, max_tokens_per_rank=S)
+    gen = torch.Generator().manual_seed(11)
+    ids, wts = wl.routing(W, S, shape.topk, wl.popularity(shape.num_experts, 0.0, gen), gen)
+    layers, rts = make_local_layers(cfg, ids, ids, wait_limit_ms=500)
+    W1, W2 = _weights(shape)
+    for l in layers:
+        l.load_weights(lambda e: W1[e], lambda e: W2[e])
+    idc, wtc = [ids[r].cuda() for r in range(W)], [wts[r].cuda() for r in range(W)]
+    outs = []
+    for step in (0, 1, 0):
+        xs = [wl.tokens(r, S, shape.hidden, seed=step) for r in range(W)]
+        ys = local_step(layers, idc, wtc, [x.cuda() for x in xs])
+        refs = _reference(xs, ids, wts, W1, W2)
+        for r in range(W):
+            _close(ys[r], refs[r], f"step {step} rank {r}")
+        outs.append([y.clone() for y in ys])
+    for r in range(W):
+        assert torch.equal(outs[0][r], outs[2][r])
+        assert not torch.equal(outs[0][r], outs[1][r])
+    for l in layers:
+        l.check()
+        l.close()
+    for rt in rts:
+        rt.destroy()
+
+
+def test_capacity_violation_is_reported_not_faulted():
+    """A receive capacity one row short of the demand: the device mask names the buffers, the GEMMs
+    compute nothing, the host raises CapacityExceeded and the context stays usable."""
+    shape, S = SMALL, 32
+    cfg = EPMoEConfig(shape=shape, ranks=1, ranks_per_node=1, max_tokens_per_rank=S)
+    gen = torch.Generator().manual_seed(0)
+    ids, wts = wl.routing(1, S, shape.topk, wl.popularity(shape.num_experts, 0.0, gen), gen)
+    tight = Capacities(*([S * shape.topk - 1] * 8))
+    import zepp_b200.layer as zl
+    orig = zl.compute_capacities
+    zl.compute_capacities = lambda *a, **k: tight
+    try:
+        layer = EPMoE(cfg, LocalGroup(0, 1), ids, ids)
+    finally:
+        zl.compute_capacities = orig
+    W1, W2 = _weights(shape)
+    layer.load_weights(lambda e: W1[e], lambda e: W2[e])
+    plan = layer.prepare(ids[0].cuda(), wts[0].cuda())
+    y = layer.forward(wl.tokens(0, S, shape.hidden).cuda(), plan)
+    with pytest.raises(CapacityExceeded) as ei:
+        layer.check()
+    assert {f for f, _, _ in ei.value.violations} >= {"recv_cap", "combine_send"}
+    assert float(y.float().abs().max()) == 0.0
+    assert float(torch.ones(3, device="cuda").sum()) == 3.0
+    layer.close()
+
+
+def test_benchmark_shape_one_rank_of_eight():
+    """Qwen3-30B layer shape, 8-way sharding emulated on one GPU at 64 tokens per rank (full H, I, E)."""
+    shape = dataclasses.replace(wl.shape_of("qwen3-30b"))
+    _run_local(shape, 8, 8, 64, "overlap", steps=1, check_plan=False)

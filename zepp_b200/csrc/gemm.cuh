@@ -1,0 +1,402 @@
+// Grouped expert GEMMs of the MoE layer on tcgen05 / TMEM (sm_100a).
+//
+// Both GEMMs run "weights on the M side": the 128 rows of an MMA tile are 128 output features
+// (rows of an expert's weight matrix, K-major as stored), the N side is a tile of up to 128 routed
+// token rows of that expert (also K-major), so tiny per-expert row counts (decode, 32 rows per
+// expert at 512 tokens per rank) still use full-height MMA tiles and the kernel streams each weight
+// panel exactly once per token tile.  D[feature, token] accumulates in TMEM in fp32.
+//
+//   dispatch GEMM  (replaces src/dispatch/cutlass_impls/ag_scatter_gemm_grouped_with_absmax.h:420-731
+//                   + python/zepp/layer.py:20-27): gate and up tiles of W1 share one token tile and
+//                   accumulate into two TMEM regions; the epilogue applies SwiGLU and writes bf16
+//                   activations [row, I].
+//   combine GEMM   (replaces src/combine/cutlass_impls/gather_rs_gemm_grouped_with_absmax.h and
+//                   src/combine/combine_kernels.cu:106-304): W2 tile x activation tile; the epilogue
+//                   multiplies by the copy's top-k weight and stores the bf16 row slice straight into
+//                   the home rank's [S, K, H] slot panel (a peer-mapped pointer over NVLink).
+//
+// One persistent CTA per SM, 6 warps: warp 0 = TMA producer, warp 1 = MMA issuer (owns TMEM),
+// warps 2..5 = epilogue (one TMEM lane quadrant each).  Optional warps 6..9 (dispatch GEMM, fused
+// mode) pull routed token rows from the source ranks' symmetric x buffers into the local receive
+// buffer, tile by tile in schedule order, and publish per-tile ready counters that the producer
+// waits on before it issues the tile's TMA loads.
+#pragma once
+#include "common.cuh"
+
+namespace zepp {
+
+constexpr int kTileM = 128;       // output features per MMA tile (TMEM lanes)
+constexpr int kTileN = 128;       // max token rows per tile (TMEM columns per accumulator)
+constexpr int kTileK = 64;        // bf16 elements per smem row = 128 bytes = one swizzle row
+constexpr int kWTileBytes = kTileM * kTileK * 2;   // 16 KB
+constexpr int kXTileBytes = kTileN * kTileK * 2;   // 16 KB
+constexpr int kAccStages = 2;
+
+enum GemmMode : int { MODE_GATE_UP_SWIGLU = 0, MODE_SINGLE_GELU = 1, MODE_DOWN_COMBINE = 2 };
+
+// Per-step tables written by the metadata kernels (device memory; nothing is read on the host).
+struct TileTables {
+  const int* n_tiles;      // [1] token tiles of this rank's experts this step
+  const int* tile_group;   // [max_tiles] local group (1..gpe-1) of the tile
+  const int* tile_row0;    // [max_tiles] first row of the tile in the receive / activation buffer
+  const int* tile_rows;    // [max_tiles] valid rows (1..128)
+};
+
+struct GemmArgs {
+  TileTables tt;
+  int k_extent;            // H (dispatch GEMM) or I (combine GEMM)
+  int n_feat_tiles;        // feature tiles per expert: I/128 or H/128
+  int w_rows_per_group;    // rows of one expert's weight matrix: 2I, I or H
+  int up_row_offset;       // I for gate|up, unused otherwise
+  // dispatch GEMM output
+  __nv_bfloat16* act;      // [cap, ld_act]
+  int ld_act;
+  // combine GEMM epilogue
+  const float* row_scale;          // [cap] top-k weight of the copy in row r
+  const long long* row_dst;        // [cap] home * 2^40 + element offset into the home's panel
+  __nv_bfloat16* const* panels;    // [W] peer-mapped slot panels [S*K, H]
+  __nv_bfloat16* staging;          // unfused combine: rows go to staging[r, H] instead of the panels
+  // completion signal of the combine GEMM (last CTA stores `epoch` into every peer's flag[rank])
+  unsigned long long* const* done_flags;   // [W] peer-mapped flag arrays, or nullptr
+  unsigned int* cta_counter;               // self-resetting arrival counter
+  int world, rank;
+  unsigned long long epoch;
+  // fused gather (dispatch GEMM, overlap strategy)
+  const int* row_tok;                      // [cap] global token id (source * S + token) of row r
+  const __nv_bfloat16* const* x_ptrs;      // [W] peer-mapped x buffers [S, H]
+  const __nv_bfloat16* x_self;             // this rank's own x (read in place), or nullptr
+  const unsigned long long* x_flags;       // [W] local flags: x of source s published for `epoch`
+  __nv_bfloat16* recv;                     // [cap, H] local receive buffer (TMA source)
+  unsigned int* tile_ready;                // [max_tiles] rows landed per tile (zeroed per step)
+  int tokens_per_rank;
+  int gather;                              // 1: run the gather warps and gate tiles on tile_ready
+  // bounded waits
+  unsigned long long* status;
+  unsigned int mbar_limit;
+  unsigned long long flag_limit_ns;
+};
+
+template <int MODE>
+struct GemmCfg {
+  static constexpr bool kDual = (MODE == MODE_GATE_UP_SWIGLU);
+  static constexpr int kStageBytes = (kDual ? 2 : 1) * kWTileBytes + kXTileBytes;
+  static constexpr int kStages = kDual ? 4 : 6;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024;   // + alignment slack
+  static constexpr int kAccCols = kDual ? 2 * kTileN : kTileN;      // TMEM columns per accumulator stage
+  static constexpr int kTmemCols = kAccStages * kAccCols;           // 512 or 256
+};
+
+__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+// SwiGLU with the reference's rounding points (python/zepp/layer.py:20-27 on bf16 tensors;
+// src/planner/lane_device.cu:476-501): both GEMM outputs are bf16, s = bf16(g / (1 + exp(-g))),
+// out = bf16(float(s) * float(u)).
+__device__ __forceinline__ __nv_bfloat16 swiglu_bf16(float gate_acc, float up_acc) {
+  const float g = bf16_round(gate_acc);
+  const float u = bf16_round(up_acc);
+  const float s = bf16_round(g / (1.0f + __expf(-g)));
+  return __float2bfloat16_rn(s * u);
+}
+__device__ __forceinline__ __nv_bfloat16 gelu_bf16(float acc) {
+  const float h = bf16_round(acc);
+  return __float2bfloat16_rn(0.5f * h * (1.0f + erff(h * 0.70710678118654752f)));
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(320, 1)
+moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x32,
+                const __grid_constant__ CUtensorMap tm_x64, const __grid_constant__ CUtensorMap tm_x128,
+                const GemmArgs a) {
+  using Cfg = GemmCfg<MODE>;
+  constexpr int STAGES = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+
+  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  __shared__ __align__(8) uint64_t acc_full_bar[kAccStages];
+  __shared__ __align__(8) uint64_t acc_empty_bar[kAccStages];
+  __shared__ uint32_t tmem_base_smem;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const bool violation = a.status != nullptr && a.status[ST_VIOLATION] != 0ull;
+  const int n_tiles = violation ? 0 : *a.tt.n_tiles;     // a step over capacity computes nothing
+  const int total_items = n_tiles * a.n_feat_tiles;
+  const int k_blocks = a.k_extent / kTileK;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < kAccStages; ++s) {
+      mbar_init(&acc_full_bar[s], 1);
+      mbar_init(&acc_empty_bar[s], 4);       // one arrival per epilogue warp
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_base_smem, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tm_w);
+    tma_prefetch_desc(&tm_x32);
+    tma_prefetch_desc(&tm_x64);
+    tma_prefetch_desc(&tm_x128);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_smem;
+  volatile int* abortp = &abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int item = blockIdx.x; item < total_items && !*abortp; item += gridDim.x) {
+        const int ti = item / a.n_feat_tiles;
+        const int j = item - ti * a.n_feat_tiles;
+        const int grp = a.tt.tile_group[ti];
+        const int row0 = a.tt.tile_row0[ti];
+        const int rows = a.tt.tile_rows[ti];
+        const CUtensorMap* tmx = rows <= 32 ? &tm_x32 : (rows <= 64 ? &tm_x64 : &tm_x128);
+        const uint32_t x_bytes = (rows <= 32 ? 32u : (rows <= 64 ? 64u : 128u)) * (kTileK * 2);
+        const uint32_t tx = (Cfg::kDual ? 2u : 1u) * kWTileBytes + x_bytes;
+        const int w_row = grp * a.w_rows_per_group + j * kTileM;
+        if (MODE != MODE_DOWN_COMBINE && a.gather) {
+          // rows of this tile are pulled by gather warps (of any CTA): wait until all have landed
+          const unsigned long long t0 = globaltimer_ns();
+          bool ok = true;
+          while (ld_acquire_gpu_u32(a.tile_ready + ti) < (unsigned int)rows) {
+            if (*abortp || globaltimer_ns() - t0 > a.flag_limit_ns) { ok = false; break; }
+            __nanosleep(64);
+          }
+          if (!ok) {
+            record_timeout(a.status, WAIT_TILE_READY, ti, (long long)a.epoch);
+            abort_flag = 1;
+            break;
+          }
+          fence_proxy_async();      // generic-proxy writes of the gather -> async-proxy TMA reads
+        }
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abortp, a.mbar_limit)) {
+            record_timeout(a.status, WAIT_MBAR_EMPTY, item, kb);
+            abort_flag = 1;
+            break;
+          }
+          uint8_t* st = smem + stage * Cfg::kStageBytes;
+          mbar_expect_tx(&full_bar[stage], tx);
+          tma_load_2d(st, &tm_w, &full_bar[stage], kb * kTileK, w_row);
+          if (Cfg::kDual) tma_load_2d(st + kWTileBytes, &tm_w, &full_bar[stage], kb * kTileK, w_row + a.up_row_offset);
+          tma_load_2d(st + (Cfg::kDual ? 2 : 1) * kWTileBytes, tmx, &full_bar[stage], kb * kTileK, row0);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      for (int item = blockIdx.x; item < total_items && !*abortp; item += gridDim.x) {
+        const int ti = item / a.n_feat_tiles;
+        const int rows = a.tt.tile_rows[ti];
+        const uint32_t n_mma = (uint32_t)((rows + 15) & ~15);
+        const uint32_t idesc = make_idesc_bf16_m128(n_mma);
+        if (!mbar_wait_bounded(&acc_empty_bar[acc], acc_phase ^ 1, abortp, a.mbar_limit)) {
+          record_timeout(a.status, WAIT_TMEM_EMPTY, item, acc);
+          abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d0 = tmem_base + acc * Cfg::kAccCols;
+        bool ok = true;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait_bounded(&full_bar[stage], phase, abortp, a.mbar_limit)) {
+            record_timeout(a.status, WAIT_MBAR_FULL, item, kb);
+            abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t st = smem_u32(smem + stage * Cfg::kStageBytes);
+          const uint64_t w0 = make_kmajor_sw128_desc(st);
+          const uint64_t w1 = make_kmajor_sw128_desc(st + kWTileBytes);
+          const uint64_t xd = make_kmajor_sw128_desc(st + (Cfg::kDual ? 2 : 1) * kWTileBytes);
+#pragma unroll
+          for (int k = 0; k < kTileK / 16; ++k) {
+            const uint32_t accum = (kb | k) != 0 ? 1u : 0u;
+            umma_bf16(d0, w0 + 2 * k, xd + 2 * k, idesc, accum);
+            if (Cfg::kDual) umma_bf16(d0 + kTileN, w1 + 2 * k, xd + 2 * k, idesc, accum);
+          }
+          umma_commit(&empty_bar[stage]);       // stage reusable once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&acc_full_bar[acc]);        // accumulator complete
+        if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+    __syncwarp();
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ epilogue (4 warps)
+    const int quad = warp & 3;                  // TMEM lane quadrant this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+      const int ti = item / a.n_feat_tiles;
+      const int j = item - ti * a.n_feat_tiles;
+      const int row0 = a.tt.tile_row0[ti];
+      const int rows = a.tt.tile_rows[ti];
+      int got = 0;
+      if (lane == 0) got = mbar_wait_bounded(&acc_full_bar[acc], acc_phase, abortp, a.mbar_limit) ? 1 : 0;
+      got = __shfl_sync(0xffffffffu, got, 0);
+      if (!got) {
+        if (lane == 0 && !*abortp) {
+          record_timeout(a.status, WAIT_TMEM_FULL, item, acc);
+          abort_flag = 1;
+        }
+        break;
+      }
+      tc_fence_after();
+      const uint32_t t0 = tmem_base + acc * Cfg::kAccCols + ((uint32_t)(quad * 32) << 16);
+      const int feat = j * kTileM + quad * 32 + lane;       // output feature of this thread
+      for (int c0 = 0; c0 < rows; c0 += 32) {
+        uint32_t g[32];
+        tmem_ld_32x32(t0 + c0, g);
+        if (MODE == MODE_GATE_UP_SWIGLU) {
+          uint32_t u[32];
+          tmem_ld_32x32(t0 + kTileN + c0, u);
+          tmem_ld_wait();
+          __nv_bfloat16* out = a.act + (size_t)(row0 + c0) * a.ld_act + feat;
+#pragma unroll
+          for (int n = 0; n < 32; ++n)
+            if (c0 + n < rows) out[(size_t)n * a.ld_act] = swiglu_bf16(__uint_as_float(g[n]), __uint_as_float(u[n]));
+        } else if (MODE == MODE_SINGLE_GELU) {
+          tmem_ld_wait();
+          __nv_bfloat16* out = a.act + (size_t)(row0 + c0) * a.ld_act + feat;
+#pragma unroll
+          for (int n = 0; n < 32; ++n)
+            if (c0 + n < rows) out[(size_t)n * a.ld_act] = gelu_bf16(__uint_as_float(g[n]));
+        } else {
+          tmem_ld_wait();
+          // lane n holds the routing of row c0 + n; broadcast per column
+          float my_scale = 0.f;
+          long long my_dst = -1;
+          if (c0 + lane < rows) {
+            my_scale = a.row_scale[row0 + c0 + lane];
+            my_dst = a.row_dst[row0 + c0 + lane];
+          }
+#pragma unroll
+          for (int n = 0; n < 32; ++n) {
+            const float sc = __shfl_sync(0xffffffffu, my_scale, n);
+            const long long dst = __shfl_sync(0xffffffffu, my_dst, n);
+            if (dst >= 0) {
+              // reference rounding points (combine_kernels.cu:191-197): bf16 GEMM output, fp32
+              // product with the top-k weight, bf16 row on the wire
+              const float v = bf16_round(__uint_as_float(g[n])) * sc;
+              __nv_bfloat16* out = a.staging != nullptr
+                                       ? a.staging + (size_t)(row0 + c0 + n) * a.w_rows_per_group
+                                       : a.panels[(int)(dst >> 40)] + (size_t)(dst & ((1ll << 40) - 1));
+              out[feat] = __float2bfloat16_rn(v);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
+      if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
+    }
+  } else {
+    // ------------------------------------------------------------------ gather warps (fused dispatch)
+    if (MODE != MODE_DOWN_COMBINE && a.gather) {
+      const int gw = warp - 6;                  // 0..3
+      // every source must have published its x for this step
+      bool ok = true;
+      if (a.x_flags != nullptr && lane < a.world) {
+        if (!wait_epoch_geq(a.x_flags + lane, a.epoch, a.flag_limit_ns)) {
+          record_timeout(a.status, WAIT_X, lane, (long long)a.epoch);
+          ok = false;
+        }
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) abort_flag = 1;
+      } else {
+        // rows are pulled in schedule order (tile by tile, the order the GEMM consumes them); row q of
+        // the step goes to gather warp (q mod all gather warps), so every SM keeps loads in flight
+        const int vec_per_row = a.k_extent / 8;                 // 16-byte vectors per row
+        const int n_warps = gridDim.x * 4;
+        const int my_warp = blockIdx.x * 4 + gw;
+        int base = 0;
+        for (int ti = 0; ti < n_tiles; ++ti) {
+          const int row0 = a.tt.tile_row0[ti];
+          const int rows = a.tt.tile_rows[ti];
+          int first = (my_warp - base) % n_warps;
+          if (first < 0) first += n_warps;
+          base += rows;
+          for (int r = first; r < rows; r += n_warps) {
+            const int tok = a.row_tok[row0 + r];
+            const int src = tok / a.tokens_per_rank;
+            const int t = tok - src * a.tokens_per_rank;
+            if (tok >= 0 && src < a.world) {
+              const __nv_bfloat16* xb = (src == a.rank && a.x_self != nullptr) ? a.x_self : a.x_ptrs[src];
+              const uint4* sp = reinterpret_cast<const uint4*>(xb + (size_t)t * a.k_extent);
+              uint4* dp = reinterpret_cast<uint4*>(a.recv + (size_t)(row0 + r) * a.k_extent);
+              for (int v0 = 0; v0 < vec_per_row; v0 += 32 * 8) {
+                uint4 buf[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                  const int v = v0 + q * 32 + lane;
+                  if (v < vec_per_row) buf[q] = sp[v];
+                }
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                  const int v = v0 + q * 32 + lane;
+                  if (v < vec_per_row) dp[v] = buf[q];
+                }
+              }
+            } else if (lane == 0 && a.status != nullptr) {
+              atomicOr(a.status + ST_ERROR, (unsigned long long)ERR_BAD_INDEX);
+            }
+            __threadfence();
+            __syncwarp();
+            if (lane == 0) atomicAdd(a.tile_ready + ti, 1u);
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+  if (MODE == MODE_DOWN_COMBINE && a.done_flags != nullptr) {
+    // all of this CTA's panel stores are ordered before its arrival; the last CTA publishes the epoch
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const unsigned int prev = atomicInc(a.cta_counter, gridDim.x - 1);
+      if (prev == gridDim.x - 1) {
+        __threadfence_system();
+        for (int p = 0; p < a.world; ++p) st_release_sys(a.done_flags[p] + a.rank, a.epoch);
+      }
+    }
+  }
+}
+
+}  // namespace zepp

@@ -1,0 +1,135 @@
+// Data-movement kernels around the two GEMMs: publication of x, the unfused dispatch pull and
+// combine push of the `direct` strategy (comparison point; the reference's is
+// python/zepp/comm/direct.py:184-213 over src/direct/all2all_single_2d_impl.cu), and the
+// per-token top-k reduction (src/combine/combine_kernels.cu:440-478).
+#pragma once
+#include "common.cuh"
+#include "planner.cuh"
+
+namespace zepp {
+
+// x [S, H] -> this rank's symmetric buffer, then `epoch` into every rank's x_flags[rank].
+__global__ void publish_x_kernel(const uint4* __restrict__ x, uint4* __restrict__ xsym, size_t n_vec, int rank,
+                                 int world, PeerTable flags, unsigned long long epoch, unsigned int* counter) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (size_t)gridDim.x * blockDim.x)
+    xsym[i] = x[i];
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicInc(counter, gridDim.x - 1);
+    if (prev == gridDim.x - 1) {
+      __threadfence_system();
+      for (int p = 0; p < world; ++p)
+        st_release_sys(reinterpret_cast<unsigned long long*>(flags.ptr[p]) + rank, epoch);
+    }
+  }
+}
+
+struct MoveArgs {
+  const int* m_this;                       // [2] rows, first global row
+  const int* row_tok;                      // [cap]
+  const long long* row_dst;                // [cap]
+  const __nv_bfloat16* const* x_ptrs;      // [W] symmetric x buffers
+  const __nv_bfloat16* x_self;             // this rank's x (read directly)
+  __nv_bfloat16* recv;                     // [cap, H]
+  const __nv_bfloat16* staging;            // [cap, H]
+  __nv_bfloat16* const* panels;            // [W]
+  unsigned long long* const* done_flags;   // [W]
+  const unsigned long long* x_flags;       // [W]
+  unsigned int* counter;
+  int H, S, world, rank, recv_cap;
+  unsigned long long epoch, limit_ns;
+  unsigned long long* status;
+};
+
+__device__ __forceinline__ void copy_row_warp(const uint4* sp, uint4* dp, int vec_per_row, int lane) {
+  for (int v0 = 0; v0 < vec_per_row; v0 += 32 * 8) {
+    uint4 buf[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const int v = v0 + q * 32 + lane;
+      if (v < vec_per_row) buf[q] = sp[v];
+    }
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const int v = v0 + q * 32 + lane;
+      if (v < vec_per_row) dp[v] = buf[q];
+    }
+  }
+}
+
+// recv[r] = x of row r's source token, pulled over NVLink (one warp per row).
+__global__ void dispatch_pull_kernel(MoveArgs a) {
+  if (!block_wait_all(a.x_flags, a.world, a.epoch, a.limit_ns, a.status, WAIT_X)) return;
+  if (a.status[ST_VIOLATION] != 0ull) return;
+  const int m = min(a.m_this[0], a.recv_cap);
+  const int lane = threadIdx.x & 31;
+  const int wpb = blockDim.x >> 5;
+  for (int r = blockIdx.x * wpb + (threadIdx.x >> 5); r < m; r += gridDim.x * wpb) {
+    const int tok = a.row_tok[r];
+    const int src = tok / a.S;
+    const int t = tok - src * a.S;
+    if (tok < 0 || src >= a.world) continue;
+    const __nv_bfloat16* base = (src == a.rank && a.x_self != nullptr) ? a.x_self : a.x_ptrs[src];
+    copy_row_warp(reinterpret_cast<const uint4*>(base + (size_t)t * a.H),
+                  reinterpret_cast<uint4*>(a.recv + (size_t)r * a.H), a.H / 8, lane);
+  }
+}
+
+// staging[r] -> the home rank's slot panel, then the completion epoch to every rank.
+__global__ void combine_push_kernel(MoveArgs a) {
+  const int m = a.status[ST_VIOLATION] != 0ull ? 0 : min(a.m_this[0], a.recv_cap);
+  const int lane = threadIdx.x & 31;
+  const int wpb = blockDim.x >> 5;
+  for (int r = blockIdx.x * wpb + (threadIdx.x >> 5); r < m; r += gridDim.x * wpb) {
+    const long long dst = a.row_dst[r];
+    const int home = (int)(dst >> 40);
+    if (dst < 0 || home >= a.world) continue;
+    copy_row_warp(reinterpret_cast<const uint4*>(a.staging + (size_t)r * a.H),
+                  reinterpret_cast<uint4*>(a.panels[home] + (size_t)(dst & ((1ll << 40) - 1))), a.H / 8, lane);
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicInc(a.counter, gridDim.x - 1);
+    if (prev == gridDim.x - 1) {
+      __threadfence_system();
+      for (int p = 0; p < a.world; ++p) st_release_sys(a.done_flags[p] + a.rank, a.epoch);
+    }
+  }
+}
+
+// y[t] = bf16( sum_k float(panel[t, k]) ), once every rank's combine rows have landed.
+__global__ void combine_reduce_kernel(const __nv_bfloat16* __restrict__ panel, __nv_bfloat16* __restrict__ y, int S,
+                                      int K, int H, const unsigned long long* done_flags, int world,
+                                      unsigned long long epoch, unsigned long long limit_ns,
+                                      unsigned long long* status) {
+  if (!block_wait_all(done_flags, world, epoch, limit_ns, status, WAIT_COMBINE)) return;
+  const int vec_per_row = H / 8;
+  const size_t total = (size_t)S * vec_per_row;
+  const bool dead = status[ST_VIOLATION] != 0ull;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / vec_per_row;
+    const int v = (int)(i - t * vec_per_row);
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (!dead) {
+      for (int k = 0; k < K; ++k) {
+        const uint4 raw = reinterpret_cast<const uint4*>(panel + ((size_t)t * K + k) * H)[v];
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float2 f = __bfloat1622float2(h2[q]);
+          acc[2 * q] += f.x;
+          acc[2 * q + 1] += f.y;
+        }
+      }
+    }
+    uint4 out;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) o2[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
+    reinterpret_cast<uint4*>(y + t * H)[v] = out;
+  }
+}
+
+}  // namespace zepp

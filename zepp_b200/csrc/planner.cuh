@@ -1,0 +1,424 @@
+// Integer planning kernels: per-expert demand histogram + exchange, capacity-constrained replica
+// routing (rotation water-fill, budgets, deterministic ordinal assignment, per-token vacate) and
+// the routing exchange.  All results are pure integer functions of replicated inputs, so every
+// rank derives identical tables; they are bit-exact against the reference's host planner
+// (python/zepp/routing.py), not against its device router, whose per-entry assignment uses
+// relaxed atomic tickets (src/planner/routing.cu:247,448).
+#pragma once
+#include "common.cuh"
+
+namespace zepp {
+
+constexpr int kMaxRep = 32;      // replicas of one expert the tables hold (reference: K_MAX_REP)
+constexpr int kMaxRanks = 64;
+
+__host__ __device__ inline int route_cm(int R) { return R < kMaxRep ? R : kMaxRep; }
+
+// Route workspace layout (int32 words).
+struct RouteWs {
+  int rep, rphys, c, D, U, Lb, fill, M, rel, ext, total;
+};
+__host__ __device__ inline RouteWs route_ws_layout(int G, int R) {
+  const int CM = route_cm(R);
+  RouteWs w;
+  int o = 0;
+  w.rep = o;   o += G * CM;        // host rank of replica jj (ascending), -1 pad
+  w.rphys = o; o += G * CM;        // physical slot of replica jj
+  w.c = o;     o += G;             // replica count
+  w.D = o;     o += G;             // global demand
+  w.U = o;     o += G;             // upper bound per replica
+  w.Lb = o;    o += G;             // lower bound per replica
+  w.fill = o;  o += G * CM;        // rows on replica jj after the water-fill
+  w.M = o;     o += G * R * CM;    // takes M[g][i][jj]
+  w.rel = o;   o += G * CM;        // release budget of this source
+  w.ext = o;   o += G * CM;        // extra budget of this source
+  w.total = o;
+  return w;
+}
+
+struct PeerTable {
+  void* ptr[kMaxRanks];
+};
+
+// ---------------------------------------------------------------------------------------
+// loads: d_own[G] = bincount(topk_own) and its publication to every rank
+// (python/zepp/planner.py:104-112: index_add_ + all_gather_into_tensor).
+// One block.  dst.ptr[p] is rank p's loads table [R, G]; flags.ptr[p] its arrival words [R].
+// ---------------------------------------------------------------------------------------
+__global__ void loads_publish_kernel(const int* __restrict__ topk_own, int n_entries, int G, int rank, int world,
+                                     PeerTable dst, PeerTable flags, unsigned long long epoch,
+                                     unsigned long long* status) {
+  extern __shared__ int hist[];
+  for (int g = threadIdx.x; g < G; g += blockDim.x) hist[g] = 0;
+  __syncthreads();
+  for (int n = threadIdx.x; n < n_entries; n += blockDim.x) {
+    const int g = topk_own[n];
+    if (g >= 0 && g < G) atomicAdd(&hist[g], 1);
+    else if (status) atomicOr(status + ST_ERROR, (unsigned long long)ERR_BAD_INDEX);
+  }
+  __syncthreads();
+  for (int p = 0; p < world; ++p) {
+    int* row = reinterpret_cast<int*>(dst.ptr[p]) + (size_t)rank * G;
+    for (int g = threadIdx.x; g < G; g += blockDim.x) row[g] = hist[g];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < world && flags.ptr[threadIdx.x] != nullptr)
+    st_release_sys(reinterpret_cast<unsigned long long*>(flags.ptr[threadIdx.x]) + rank, epoch);
+}
+
+// Thread 0 of a block waits until every rank's word in `flags` reached `epoch`.
+__device__ __forceinline__ bool block_wait_all(const unsigned long long* flags, int world, unsigned long long epoch,
+                                               unsigned long long limit_ns, unsigned long long* status, int what) {
+  __shared__ int ok_s;
+  if (threadIdx.x == 0) ok_s = 1;
+  __syncthreads();
+  if (flags != nullptr && threadIdx.x < world) {
+    if (!wait_epoch_geq(flags + threadIdx.x, epoch, limit_ns)) {
+      record_timeout(status, what, threadIdx.x, (long long)epoch);
+      ok_s = 0;
+    }
+  }
+  __syncthreads();
+  return ok_s != 0;
+}
+
+__device__ __forceinline__ long long ceil_div_ll(long long a, long long b) { return (a + b - 1) / b; }
+
+// ---------------------------------------------------------------------------------------
+// route: one warp per expert.
+//   lane 0   replica table (ascending host rank), bounds U / Lb, R-round rotation water-fill
+//            (python/zepp/routing.py:80-119; device twin src/planner/routing.cu:75-234);
+//   lanes    release / extra budgets of this source per replica by largest remainder
+//            (routing.py:189-225);
+//   warp     deterministic ordinal assignment of this source's entries (routing.py:146-186):
+//            the o-th entry of expert g in flat (token, k) order goes to the visit-ordered
+//            segment that contains o.  Ordinals come from ballots over the entry stream.
+// ---------------------------------------------------------------------------------------
+struct RouteArgs {
+  const int* topk_own;      // [S*K]
+  int n_entries;
+  const int* loads;         // [R, G]
+  const int* l2p;           // [G, R]
+  const int* lcnts;         // [G]
+  int G, R, L, nlp, my_rank;
+  long long c_num, c_den;
+  int* ws;
+  int* phys_own;            // [S*K]
+  const unsigned long long* loads_flags;   // [R] or nullptr
+  unsigned long long epoch;
+  unsigned long long limit_ns;
+  unsigned long long* status;
+  long long* stats;         // [4]: 0 stranded rows, 1 vacate moves, 2 ordinal overflow, 3 unused
+};
+
+__global__ void __launch_bounds__(256) route_kernel(RouteArgs a) {
+  if (!block_wait_all(a.loads_flags, a.R, a.epoch, a.limit_ns, a.status, WAIT_LOADS)) return;
+  const int warps_per_block = blockDim.x >> 5;
+  const int wib = threadIdx.x >> 5;
+  const int g = blockIdx.x * warps_per_block + wib;
+  const int lane = threadIdx.x & 31;
+  if (g >= a.G) return;
+  const int R = a.R, L = a.L, NN = R / L, G = a.G;
+  const int CM = route_cm(R);
+  const RouteWs w = route_ws_layout(G, R);
+  int* rep = a.ws + w.rep + g * CM;
+  int* rphys = a.ws + w.rphys + g * CM;
+  int* fillp = a.ws + w.fill + g * CM;
+  int* Mg = a.ws + w.M + (size_t)g * R * CM;
+  int* relp = a.ws + w.rel + g * CM;
+  int* extp = a.ws + w.ext + g * CM;
+  __shared__ int left_s[8][kMaxRanks];
+  __shared__ long long fill_s[8][kMaxRep];
+  __shared__ int cum_s[8][kMaxRep];
+  __shared__ int vphys_s[8][kMaxRep];
+  int* left = left_s[wib];
+  long long* fill = fill_s[wib];
+
+  // ---- replica table + bounds + water-fill (lane 0)
+  int c = 0;
+  long long D = 0, U = 0, Lb = 0;
+  if (lane == 0) {
+    const int cnt = min(a.lcnts[g], R);
+    for (int j = 0; j < cnt; ++j) {
+      const int p = a.l2p[g * R + j];
+      if (p >= 0 && c < CM) { rep[c] = p / a.nlp; rphys[c] = p; ++c; }
+    }
+    for (int j = c; j < CM; ++j) { rep[j] = -1; rphys[j] = -1; }
+    for (int i = 0; i < R; ++i) { left[i] = a.loads[i * G + g]; D += left[i]; }
+    if (c > 0) {
+      U = ceil_div_ll((a.c_den + a.c_num) * D, a.c_den * c);
+      Lb = ((a.c_den - a.c_num) * D) / (a.c_den * c);
+    }
+    for (int j = 0; j < CM; ++j) fill[j] = 0;
+    for (int i = 0; i < R; ++i)
+      for (int j = 0; j < CM; ++j) Mg[i * CM + j] = 0;
+    long long unassigned = D;
+    for (int p = 0; p < R && c > 0; ++p) {
+      const int du = p / L, dl = p % L;
+      for (int jj = 0; jj < c; ++jj) {
+        const int j = rep[jj];
+        const int i = ((((j / L) - du) % NN + NN) % NN) * L + ((((j % L) - dl) % L + L) % L);
+        long long def_others = 0;
+        for (int k = 0; k < c; ++k)
+          if (k != jj && Lb > fill[k]) def_others += Lb - fill[k];
+        long long take = left[i];
+        if (U - fill[jj] < take) take = U - fill[jj];
+        if (unassigned - def_others < take) take = unassigned - def_others;
+        if (take < 0) take = 0;
+        Mg[i * CM + jj] = (int)take;
+        fill[jj] += take;
+        left[i] -= (int)take;
+        unassigned -= take;
+      }
+    }
+    if (unassigned != 0) {
+      if (a.stats) atomicAdd((unsigned long long*)a.stats + 0, (unsigned long long)unassigned);
+      if (a.status) atomicOr(a.status + ST_ERROR, (unsigned long long)ERR_ROUTE);
+    }
+    a.ws[w.c + g] = c;
+    a.ws[w.D + g] = (int)D;
+    a.ws[w.U + g] = (int)U;
+    a.ws[w.Lb + g] = (int)Lb;
+    for (int j = 0; j < CM; ++j) fillp[j] = (int)fill[j];
+  }
+  c = __shfl_sync(0xffffffffu, c, 0);
+  U = __shfl_sync(0xffffffffu, U, 0);
+  Lb = __shfl_sync(0xffffffffu, Lb, 0);
+  __syncwarp();
+
+  // ---- budgets of this source (lane jj)
+  const int me = a.my_rank;
+  if (lane < CM) {
+    long long rel = 0, ext = 0;
+    if (lane < c) {
+      const long long f = fill[lane];
+      if (f > Lb) {            // release: split fill - Lb by the takes M[g][.][jj]
+        const long long total = f - Lb;
+        long long Wsum = 0;
+        for (int k = 0; k < R; ++k) Wsum += Mg[k * CM + lane];
+        if (Wsum > 0) {
+          const long long wi = Mg[me * CM + lane];
+          long long base_sum = 0;
+          int pos = 0;
+          const long long fi = (total * wi) % Wsum;
+          for (int k = 0; k < R; ++k) {
+            const long long wk = Mg[k * CM + lane];
+            base_sum += (total * wk) / Wsum;
+            const long long fk = (total * wk) % Wsum;
+            if (fk > fi || (fk == fi && k < me)) ++pos;
+          }
+          rel = (total * wi) / Wsum + (pos < total - base_sum ? 1 : 0);
+          if (rel > wi) rel = wi;
+        }
+      }
+      if (U > f && R > 1) {    // extra: split U - fill by the demands d[.][g]
+        // (a single rank gets no extra budget: the reference's table pass consumes its demand
+        //  tensor in place when R == 1, python/zepp/routing.py:94,115,222)
+        const long long total = U - f;
+        long long Wsum = 0;
+        for (int k = 0; k < R; ++k) Wsum += a.loads[k * G + g];
+        if (Wsum > 0) {
+          const long long wi = a.loads[me * G + g];
+          long long base_sum = 0;
+          int pos = 0;
+          const long long fi = (total * wi) % Wsum;
+          for (int k = 0; k < R; ++k) {
+            const long long wk = a.loads[k * G + g];
+            base_sum += (total * wk) / Wsum;
+            const long long fk = (total * wk) % Wsum;
+            if (fk > fi || (fk == fi && k < me)) ++pos;
+          }
+          ext = (total * wi) / Wsum + (pos < total - base_sum ? 1 : 0);
+        }
+      }
+    }
+    relp[lane] = (int)rel;
+    extp[lane] = (int)ext;
+  }
+
+  // ---- visit order of this source and cumulative takes
+  if (a.topk_own == nullptr) return;
+  {
+    int pr = 1 << 30;
+    if (lane < c) {
+      const int j = rep[lane];
+      pr = ((((j / L) - (me / L)) % NN + NN) % NN) * L + ((((j % L) - (me % L)) % L + L) % L);
+    }
+    int pos = 0;
+    for (int k = 0; k < c; ++k) {
+      const int prk = __shfl_sync(0xffffffffu, pr, k);
+      if (lane < c && (prk < pr || (prk == pr && k < lane))) ++pos;
+    }
+    if (lane < c) {
+      cum_s[wib][pos] = Mg[me * CM + lane];
+      vphys_s[wib][pos] = rphys[lane];
+    }
+    __syncwarp();
+    if (lane == 0) {
+      int acc = 0;
+      for (int k = 0; k < c; ++k) { acc += cum_s[wib][k]; cum_s[wib][k] = acc; }
+    }
+    __syncwarp();
+  }
+  // ---- ordinal assignment over the entry stream
+  int base = 0;
+  for (int n0 = 0; n0 < a.n_entries; n0 += 32) {
+    const int n = n0 + lane;
+    const bool mine = n < a.n_entries && a.topk_own[n] == g;
+    const unsigned bal = __ballot_sync(0xffffffffu, mine);
+    if (mine) {
+      const int o = base + __popc(bal & ((1u << lane) - 1u));
+      int seg = 0;
+      for (int k = 0; k < c; ++k) seg += (cum_s[wib][k] <= o) ? 1 : 0;
+      if (seg < c) {
+        a.phys_own[n] = vphys_s[wib][seg];
+      } else {
+        a.phys_own[n] = c > 0 ? vphys_s[wib][c - 1] : 0;
+        if (a.stats) atomicAdd((unsigned long long*)a.stats + 2, 1ull);
+        if (a.status) atomicOr(a.status + ST_ERROR, (unsigned long long)ERR_ROUTE);
+      }
+    }
+    base += __popc(bal);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// vacate + routing exchange.
+// route_vacate_kernel: one thread runs the per-token vacate pass of this source in token order
+// with the host reference's semantics (python/zepp/routing.py:242-297: least-touched remote node
+// first, targets = home then the other touched nodes in first-touch order, all-or-nothing per
+// node, budgets paid on both replicas); launched only when the topology has more than one node.
+// route_finish_kernel: every block copies the send row [phys | weight bits]
+// (python/zepp/planner.py:122) into each rank's gather table; the last block publishes the epoch.
+// ---------------------------------------------------------------------------------------
+struct FinishArgs {
+  const int* topk_own;     // [S*K]
+  int* phys_own;           // [S*K] in/out
+  const float* probs_own;  // [S*K]
+  int S, K, G, R, L, nlp, my_rank;
+  int* ws;
+  int* send_row;           // [2*S*K] local copy of the row (may be nullptr)
+  PeerTable dst;           // rank p's gather table [R, 2*S*K]; nullptr entries skipped
+  PeerTable flags;         // rank p's arrival words [R]
+  int world;               // ranks to publish to (0: none)
+  unsigned long long epoch;
+  unsigned int* block_counter;
+  unsigned long long* status;
+  long long* stats;
+};
+
+__device__ void vacate_serial(const FinishArgs& a) {
+  const int R = a.R, L = a.L, K = a.K, nlp = a.nlp, G = a.G;
+  const int CM = route_cm(R);
+  const RouteWs w = route_ws_layout(G, R);
+  const int home = a.my_rank / L;
+  int* rel = a.ws + w.rel;
+  int* ext = a.ws + w.ext;
+  const int* rep = a.ws + w.rep;
+  const int* rphys = a.ws + w.rphys;
+  const int* cc = a.ws + w.c;
+  long long moves = 0;
+  int node_of[64];
+  int grp_node[64], grp_cnt[64];
+  int plan_k[64], plan_jo[64], plan_jt[64];
+  const int Kc = K < 64 ? K : 64;
+  for (int s = 0; s < a.S; ++s) {
+    int* ph = a.phys_own + s * K;
+    const int* tk = a.topk_own + s * K;
+    bool any_remote = false;
+    for (int k = 0; k < Kc; ++k) {
+      node_of[k] = ph[k] / nlp / L;
+      any_remote |= node_of[k] != home;
+    }
+    if (!any_remote) continue;
+    for (int guard = 0; guard < 4 * Kc + 4; ++guard) {
+      // remote nodes in first-touch order with their entry counts
+      int ng = 0;
+      for (int k = 0; k < Kc; ++k) {
+        if (node_of[k] == home) continue;
+        int q = 0;
+        while (q < ng && grp_node[q] != node_of[k]) ++q;
+        if (q == ng) { grp_node[ng] = node_of[k]; grp_cnt[ng] = 0; ++ng; }
+        ++grp_cnt[q];
+      }
+      if (ng == 0) break;
+      bool moved = false;
+      // candidates by (entry count, node id) ascending
+      unsigned long long tried = 0;
+      for (int round = 0; round < ng && !moved; ++round) {
+        int best = -1;
+        for (int q = 0; q < ng; ++q) {
+          if (tried >> q & 1ull) continue;
+          if (best < 0 || grp_cnt[q] < grp_cnt[best] || (grp_cnt[q] == grp_cnt[best] && grp_node[q] < grp_node[best]))
+            best = q;
+        }
+        tried |= 1ull << best;
+        const int n = grp_node[best];
+        int np = 0;
+        bool ok = true;
+        for (int k = 0; k < Kc && ok; ++k) {
+          if (node_of[k] != n) continue;
+          const int g = tk[k];
+          const int c = cc[g];
+          int jo = -1;
+          for (int jj = 0; jj < c; ++jj)
+            if (rphys[g * CM + jj] == ph[k]) { jo = jj; break; }
+          if (jo < 0 || rel[g * CM + jo] <= 0) { ok = false; break; }
+          int jt = -1;
+          // targets: home, then the other touched nodes in first-touch order
+          for (int ti = -1; ti < ng && jt < 0; ++ti) {
+            int m;
+            if (ti < 0) m = home;
+            else { if (ti == best) continue; m = grp_node[ti]; }
+            for (int jj = 0; jj < c; ++jj)
+              if (rep[g * CM + jj] / L == m && ext[g * CM + jj] > 0) { jt = jj; break; }
+          }
+          if (jt < 0) { ok = false; break; }
+          plan_k[np] = k; plan_jo[np] = jo; plan_jt[np] = jt; ++np;
+        }
+        if (!ok) continue;
+        for (int q = 0; q < np; ++q) {
+          const int k = plan_k[q], g = tk[k];
+          rel[g * CM + plan_jo[q]] -= 1;
+          ext[g * CM + plan_jo[q]] += 1;
+          ext[g * CM + plan_jt[q]] -= 1;
+          rel[g * CM + plan_jt[q]] += 1;
+          ph[k] = rphys[g * CM + plan_jt[q]];
+          node_of[k] = rep[g * CM + plan_jt[q]] / L;
+          ++moves;
+        }
+        moved = true;
+      }
+      if (!moved) break;
+    }
+  }
+  if (a.stats) a.stats[1] = moves;
+}
+
+__global__ void route_vacate_kernel(FinishArgs a) {
+  if (blockIdx.x == 0 && threadIdx.x == 0) vacate_serial(a);
+}
+
+__global__ void route_finish_kernel(FinishArgs a) {
+  const int SK = a.S * a.K;
+  const int* wbits = reinterpret_cast<const int*>(a.probs_own);
+  for (int n = blockIdx.x * blockDim.x + threadIdx.x; n < 2 * SK; n += gridDim.x * blockDim.x) {
+    const int v = n < SK ? a.phys_own[n] : wbits[n - SK];
+    if (a.send_row) a.send_row[n] = v;
+    for (int p = 0; p < a.world; ++p)
+      if (a.dst.ptr[p]) reinterpret_cast<int*>(a.dst.ptr[p])[(size_t)a.my_rank * 2 * SK + n] = v;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicInc(a.block_counter, gridDim.x - 1);
+    if (prev == gridDim.x - 1) {
+      __threadfence_system();
+      for (int p = 0; p < a.world; ++p)
+        if (a.flags.ptr[p]) st_release_sys(reinterpret_cast<unsigned long long*>(a.flags.ptr[p]) + a.my_rank, a.epoch);
+    }
+  }
+}
+
+}  // namespace zepp

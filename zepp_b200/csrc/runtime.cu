@@ -1,0 +1,810 @@
+// Host side of libzepp_b200.so: symmetric arena + peer mapping, the layer object, kernel launches
+// and the extern "C" entry points declared in include/zepp_b200.h.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "../../include/zepp_b200.h"
+#include "common.cuh"
+#include "gemm.cuh"
+#include "layer_kernels.cuh"
+#include "meta.cuh"
+#include "planner.cuh"
+#include "swap.cuh"
+
+using namespace zepp;
+
+// ---------------------------------------------------------------------------------------------
+// errors
+// ---------------------------------------------------------------------------------------------
+static thread_local std::string g_err;
+
+static int fail(const char* fmt, ...) {
+  char buf[1024];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  g_err = buf;
+  return 1;
+}
+
+#define CU_OK(expr)                                                                         \
+  do {                                                                                      \
+    cudaError_t _e = (expr);                                                                \
+    if (_e != cudaSuccess) return fail("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__, __LINE__); \
+  } while (0)
+
+extern "C" const char* zepp_last_error(void) { return g_err.c_str(); }
+extern "C" int zepp_abi_version(void) { return 1; }
+
+// ---------------------------------------------------------------------------------------------
+// runtime
+// ---------------------------------------------------------------------------------------------
+struct zepp_rt {
+  int rank = 0, world = 1, device = 0, sm_count = 0;
+  uint8_t* arena = nullptr;
+  size_t arena_bytes = 0, bump = 0;
+  uint8_t* peer_base[kMaxRanks] = {};
+  bool opened[kMaxRanks] = {};
+  bool peers_ready = false;
+  unsigned long long wait_ns = 4000000000ull;
+};
+
+static void* rt_alloc(zepp_rt* rt, size_t bytes, size_t align = 1024) {
+  size_t off = (rt->bump + align - 1) / align * align;
+  if (off + bytes > rt->arena_bytes) return nullptr;
+  rt->bump = off + bytes;
+  return rt->arena + off;
+}
+template <typename T>
+static T* peer_ptr(zepp_rt* rt, int p, T* local) {
+  return reinterpret_cast<T*>(rt->peer_base[p] + (reinterpret_cast<uint8_t*>(local) - rt->arena));
+}
+
+extern "C" int zepp_rt_create(int rank, int world, int device, size_t arena_bytes, zepp_rt** out) {
+  if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world) return fail("bad rank/world %d/%d", rank, world);
+  CU_OK(cudaSetDevice(device));
+  zepp_rt* rt = new (std::nothrow) zepp_rt();
+  if (!rt) return fail("out of host memory");
+  rt->rank = rank;
+  rt->world = world;
+  rt->device = device;
+  cudaDeviceProp prop;
+  CU_OK(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10) {
+    delete rt;
+    return fail("libzepp_b200 needs an sm_100 device (found sm_%d%d)", prop.major, prop.minor);
+  }
+  rt->sm_count = prop.multiProcessorCount;
+  rt->arena_bytes = (arena_bytes + 4095) / 4096 * 4096;
+  cudaError_t e = cudaMalloc(&rt->arena, rt->arena_bytes);
+  if (e != cudaSuccess) {
+    delete rt;
+    return fail("cudaMalloc of the %zu-byte arena failed: %s", arena_bytes, cudaGetErrorString(e));
+  }
+  CU_OK(cudaMemset(rt->arena, 0, rt->arena_bytes));
+  rt->peer_base[rank] = rt->arena;
+  rt->peers_ready = (world == 1);
+  *out = rt;
+  return 0;
+}
+
+extern "C" int zepp_rt_destroy(zepp_rt* rt) {
+  if (!rt) return 0;
+  cudaSetDevice(rt->device);
+  cudaDeviceSynchronize();
+  for (int p = 0; p < rt->world; ++p)
+    if (rt->opened[p]) cudaIpcCloseMemHandle(rt->peer_base[p]);
+  if (rt->arena) cudaFree(rt->arena);
+  delete rt;
+  return 0;
+}
+
+extern "C" int zepp_rt_ipc_handle(zepp_rt* rt, void* blob64) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  cudaIpcMemHandle_t h;
+  CU_OK(cudaSetDevice(rt->device));
+  CU_OK(cudaIpcGetMemHandle(&h, rt->arena));
+  memcpy(blob64, &h, 64);
+  return 0;
+}
+
+extern "C" int zepp_rt_open_peers(zepp_rt* rt, const void* blobs, int world) {
+  if (world != rt->world) return fail("open_peers: world %d != %d", world, rt->world);
+  CU_OK(cudaSetDevice(rt->device));
+  for (int p = 0; p < world; ++p) {
+    if (p == rt->rank) continue;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, reinterpret_cast<const uint8_t*>(blobs) + 64 * p, 64);
+    void* ptr = nullptr;
+    CU_OK(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    rt->peer_base[p] = reinterpret_cast<uint8_t*>(ptr);
+    rt->opened[p] = true;
+  }
+  rt->peers_ready = true;
+  return 0;
+}
+
+extern "C" int zepp_rt_link_local(zepp_rt** rts, int world) {
+  for (int r = 0; r < world; ++r) {
+    if (rts[r]->world != world || rts[r]->rank != r) return fail("link_local: runtime %d is rank %d of %d", r, rts[r]->rank, rts[r]->world);
+    if (rts[r]->device != rts[0]->device) return fail("link_local: all ranks must be on one device");
+    if (rts[r]->arena_bytes != rts[0]->arena_bytes) return fail("link_local: arena sizes differ");
+  }
+  for (int r = 0; r < world; ++r) {
+    for (int p = 0; p < world; ++p) rts[r]->peer_base[p] = rts[p]->arena;
+    rts[r]->peers_ready = true;
+  }
+  return 0;
+}
+
+extern "C" int zepp_rt_set_wait_limit_ms(zepp_rt* rt, int ms) {
+  if (ms < 1) return fail("wait limit must be >= 1 ms");
+  rt->wait_ns = (unsigned long long)ms * 1000000ull;
+  return 0;
+}
+extern "C" int zepp_rt_sm_count(zepp_rt* rt) { return rt->sm_count; }
+
+// ---------------------------------------------------------------------------------------------
+// tensor maps
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || !p) return nullptr;
+  fn = reinterpret_cast<EncodeTiledFn>(p);
+  return fn;
+}
+
+// bf16 row-major [rows, cols]; box = 64 columns (128 bytes) x box_rows, 128-byte swizzle, zero fill
+static int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail("cuTensorMapEncodeTiled is not available from the driver");
+  if (reinterpret_cast<uintptr_t>(base) % 16 != 0 || (cols * 2) % 16 != 0) return fail("tensor map: unaligned base/stride");
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed with %d (rows %llu cols %llu box %u)", (int)r,
+                                     (unsigned long long)rows, (unsigned long long)cols, box_rows);
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// layer
+// ---------------------------------------------------------------------------------------------
+struct zepp_layer {
+  zepp_rt* rt = nullptr;
+  zepp_layer_cfg cfg{};
+  int G, K, H, I, ffn1, W, L, NN, S, SK, nlp, gpe, E_virt, cap, max_tiles, tokens_per_tile, tiles_per_src;
+  unsigned long long epoch = 0;
+  int64_t launches = 0;
+  bool have_weights = false, have_placement = false;
+  // symmetric (peer-visible) buffers
+  int* loads_all[2];                 // [R, G]
+  int* xchg_all[2];                  // [R, 2*SK]
+  unsigned long long *loads_flags, *routing_flags, *x_flags, *done_flags;   // [R] each
+  __nv_bfloat16* xsym[2];            // [S, H]
+  __nv_bfloat16* panel;              // [S*K, H]
+  // local buffers
+  __nv_bfloat16 *recv, *act, *staging;
+  int *topk_own, *phys_own, *send_row, *route_ws, *p2l, *l2p, *lcnts, *p2l_try, *l2p_try;
+  float* probs_own;
+  long long* route_stats;
+  int *vce, *splits, *scatter_index, *sps, *uc, *tile_hist, *tile_uc, *expert_base;
+  float* probs_all;
+  long long *demands, *dplan, *cplan, *swap_block, *gate, *ovr0, *ovr1, *stag;
+  int* sched;
+  int *n_tiles, *tile_group, *tile_row0, *tile_rows, *m_this, *row_tok;
+  unsigned int *tile_ready, *counters;
+  long long* row_dst;
+  float* row_scale;
+  unsigned long long* status;
+  // device pointer tables
+  const __nv_bfloat16** x_ptrs[2];
+  __nv_bfloat16** panels;
+  unsigned long long** done_ptrs;
+  // host peer tables for the publishing kernels
+  PeerTable loads_dst[2], xchg_dst[2], loads_flag_dst, routing_flag_dst, x_flag_dst;
+  // tensor maps
+  CUtensorMap tm_w1, tm_w2, tm_recv[3], tm_act[3];
+  const void* x_self = nullptr;
+};
+
+static size_t al(size_t v) { return (v + 1023) / 1024 * 1024; }
+
+extern "C" size_t zepp_layer_arena_bytes(const zepp_layer_cfg* c) {
+  const size_t R = c->ranks, G = c->num_experts, K = c->topk, H = c->hidden, I = c->ffn_hidden, S = c->max_tokens_per_rank;
+  const size_t SK = S * K, nlp = G / R + c->redundant_slots_per_rank, gpe = nlp + 1, E = R * gpe, cap = c->caps[0];
+  const size_t tiles = (SK + 1023) / 1024 + 1;
+  size_t b = 0;
+  b += 2 * al(R * G * 4) + 2 * al(R * 2 * SK * 4) + 4 * al(R * 8) + 2 * al(S * H * 2) + al(SK * H * 2);
+  b += al(cap * H * 2) * 2 + al(cap * I * 2);
+  b += 4 * al(SK * 4) + al(2 * SK * 4) + al((size_t)zepp_route_workspace_ints((int)G, (int)R) * 4);
+  b += 3 * al(R * nlp * 4) + 2 * al(G * R * 4) + al(G * 4);
+  b += 3 * al(R * SK * 4) + al(E * 4) + al(R * E * 4) + al(R * (2 * R) * 4);
+  b += al(R * tiles * E * 4) + al(R * tiles * 2 * R * 4) + al((E + 1) * 4);
+  b += al(64 * 8) * 4 + al((size_t)zepp_swap_decide_out_ints((int)R, (int)G, (int)nlp, 8) * 8);
+  b += 8 * al(gpe * 8);
+  b += 5 * al((gpe + cap / 128 + 8) * 4) + 3 * al(cap * 8) + al(cap * 4);
+  b += 16 * al(R * 8) + (64 << 10);
+  return b + (1 << 20);
+}
+
+template <typename T>
+static int lalloc(zepp_layer* l, T** p, size_t count) {
+  *p = reinterpret_cast<T*>(rt_alloc(l->rt, count * sizeof(T)));
+  if (!*p) return fail("symmetric arena exhausted (need %zu more bytes)", count * sizeof(T));
+  return 0;
+}
+#define LA(ptr, count) \
+  if (lalloc(l, &(ptr), (size_t)(count))) return 1
+
+static int layer_alloc(zepp_layer* l) {
+  const int R = l->W;
+  // symmetric part first: identical offsets on every rank
+  for (int b = 0; b < 2; ++b) LA(l->loads_all[b], R * l->G);
+  for (int b = 0; b < 2; ++b) LA(l->xchg_all[b], (size_t)R * 2 * l->SK);
+  LA(l->loads_flags, R);
+  LA(l->routing_flags, R);
+  LA(l->x_flags, R);
+  LA(l->done_flags, R);
+  for (int b = 0; b < 2; ++b) LA(l->xsym[b], (size_t)l->S * l->H);
+  LA(l->panel, (size_t)l->SK * l->H);
+  // local part
+  LA(l->recv, (size_t)l->cap * l->H);
+  LA(l->act, (size_t)l->cap * l->I);
+  LA(l->staging, (size_t)l->cap * l->H);
+  LA(l->topk_own, l->SK);
+  LA(l->phys_own, l->SK);
+  LA(l->probs_own, l->SK);
+  LA(l->send_row, 2 * l->SK);
+  LA(l->route_ws, zepp_route_workspace_ints(l->G, R));
+  LA(l->route_stats, 4);
+  LA(l->p2l, R * l->nlp);
+  LA(l->p2l_try, R * l->nlp);
+  LA(l->l2p, l->G * R);
+  LA(l->l2p_try, l->G * R);
+  LA(l->lcnts, l->G);
+  LA(l->vce, (size_t)R * l->SK);
+  LA(l->probs_all, (size_t)R * l->SK);
+  LA(l->scatter_index, (size_t)R * l->SK);
+  LA(l->splits, l->E_virt);
+  LA(l->sps, R * l->E_virt);
+  LA(l->uc, R * (R + l->NN));
+  LA(l->tile_hist, (size_t)R * l->tiles_per_src * l->E_virt);
+  LA(l->tile_uc, (size_t)R * l->tiles_per_src * (R + l->NN));
+  LA(l->expert_base, l->E_virt + 1);
+  LA(l->demands, 8);
+  LA(l->dplan, zepp_dispatch_plan_words(l->L, l->NN));
+  LA(l->cplan, 4 * R + 2);
+  LA(l->swap_block, zepp_swap_decide_out_ints(R, l->G, l->nlp, 8));
+  LA(l->gate, 2 * l->gpe);
+  LA(l->sched, l->gpe);
+  LA(l->ovr0, l->gpe);
+  LA(l->ovr1, l->gpe);
+  LA(l->stag, 16);
+  LA(l->n_tiles, 4);
+  LA(l->tile_group, l->max_tiles);
+  LA(l->tile_row0, l->max_tiles);
+  LA(l->tile_rows, l->max_tiles);
+  LA(l->tile_ready, l->max_tiles);
+  LA(l->m_this, 4);
+  LA(l->row_tok, l->cap);
+  LA(l->row_dst, l->cap);
+  LA(l->row_scale, l->cap);
+  LA(l->counters, 16);
+  LA(l->status, ST_WORDS);
+  for (int b = 0; b < 2; ++b) LA(l->x_ptrs[b], R);
+  LA(l->panels, R);
+  LA(l->done_ptrs, R);
+  return 0;
+}
+
+extern "C" int zepp_layer_create(zepp_rt* rt, const zepp_layer_cfg* c, zepp_layer** out) {
+  if (!rt->peers_ready) return fail("layer_create: peers are not mapped yet (open_peers / link_local first)");
+  if (c->ranks != rt->world) return fail("layer_create: cfg.ranks %d != runtime world %d", c->ranks, rt->world);
+  if (c->num_experts % c->ranks) return fail("num_experts must divide by ranks");
+  if (c->ranks % c->ranks_per_node) return fail("ranks must divide by ranks_per_node");
+  if (c->hidden % 128 || c->ffn_hidden % 128) return fail("hidden and ffn_hidden must be multiples of 128 (got %d, %d)", c->hidden, c->ffn_hidden);
+  if (c->topk < 1 || c->topk > 64) return fail("topk out of range");
+  if (c->caps[0] < 1) return fail("recv_cap must be positive");
+  CU_OK(cudaSetDevice(rt->device));
+  zepp_layer* l = new (std::nothrow) zepp_layer();
+  if (!l) return fail("out of host memory");
+  l->rt = rt;
+  l->cfg = *c;
+  l->G = c->num_experts; l->K = c->topk; l->H = c->hidden; l->I = c->ffn_hidden;
+  l->ffn1 = c->act == 1 ? 2 * l->I : l->I;
+  l->W = c->ranks; l->L = c->ranks_per_node; l->NN = l->W / l->L; l->S = c->max_tokens_per_rank;
+  l->SK = l->S * l->K;
+  l->nlp = l->G / l->W + c->redundant_slots_per_rank;
+  l->gpe = l->nlp + 1;
+  l->E_virt = l->W * l->gpe;
+  l->cap = (int)c->caps[0];
+  l->max_tiles = l->gpe + l->cap / kTileRowsMax + 2;
+  l->tokens_per_tile = kMetaThreads / l->K;
+  l->tiles_per_src = (l->S + l->tokens_per_tile - 1) / l->tokens_per_tile;
+  if (l->E_virt > 4 * kMetaThreads) { delete l; return fail("too many virtual experts (%d)", l->E_virt); }
+  if (layer_alloc(l)) { delete l; return 1; }
+  // peer tables
+  const int R = l->W;
+  std::vector<const __nv_bfloat16*> xp(R);
+  std::vector<__nv_bfloat16*> pp(R);
+  std::vector<unsigned long long*> dp(R);
+  for (int b = 0; b < 2; ++b) {
+    for (int p = 0; p < R; ++p) {
+      l->loads_dst[b].ptr[p] = peer_ptr(rt, p, l->loads_all[b]);
+      l->xchg_dst[b].ptr[p] = peer_ptr(rt, p, l->xchg_all[b]);
+      xp[p] = peer_ptr(rt, p, l->xsym[b]);
+    }
+    CU_OK(cudaMemcpy(l->x_ptrs[b], xp.data(), R * sizeof(void*), cudaMemcpyHostToDevice));
+  }
+  for (int p = 0; p < R; ++p) {
+    l->loads_flag_dst.ptr[p] = peer_ptr(rt, p, l->loads_flags);
+    l->routing_flag_dst.ptr[p] = peer_ptr(rt, p, l->routing_flags);
+    l->x_flag_dst.ptr[p] = peer_ptr(rt, p, l->x_flags);
+    pp[p] = peer_ptr(rt, p, l->panel);
+    dp[p] = peer_ptr(rt, p, l->done_flags);
+  }
+  CU_OK(cudaMemcpy(l->panels, pp.data(), R * sizeof(void*), cudaMemcpyHostToDevice));
+  CU_OK(cudaMemcpy(l->done_ptrs, dp.data(), R * sizeof(void*), cudaMemcpyHostToDevice));
+  const uint32_t boxes[3] = {32, 64, 128};
+  for (int b = 0; b < 3; ++b) {
+    if (make_map(&l->tm_recv[b], l->recv, l->cap, l->H, boxes[b])) { delete l; return 1; }
+    if (make_map(&l->tm_act[b], l->act, l->cap, l->I, boxes[b])) { delete l; return 1; }
+  }
+  CU_OK(cudaFuncSetAttribute(moe_gemm_kernel<MODE_GATE_UP_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             GemmCfg<MODE_GATE_UP_SWIGLU>::kSmemBytes));
+  CU_OK(cudaFuncSetAttribute(moe_gemm_kernel<MODE_SINGLE_GELU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             GemmCfg<MODE_SINGLE_GELU>::kSmemBytes));
+  CU_OK(cudaFuncSetAttribute(moe_gemm_kernel<MODE_DOWN_COMBINE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             GemmCfg<MODE_DOWN_COMBINE>::kSmemBytes));
+  *out = l;
+  return 0;
+}
+
+extern "C" int zepp_layer_destroy(zepp_layer* l) {
+  if (l) {
+    cudaSetDevice(l->rt->device);
+    cudaDeviceSynchronize();
+    delete l;
+  }
+  return 0;
+}
+
+extern "C" int zepp_layer_set_placement(zepp_layer* l, const int32_t* p2l, const int32_t* l2p, const int32_t* lcnts,
+                                        void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  CU_OK(cudaMemcpyAsync(l->p2l, p2l, (size_t)l->W * l->nlp * 4, cudaMemcpyHostToDevice, st));
+  CU_OK(cudaMemcpyAsync(l->l2p, l2p, (size_t)l->G * l->W * 4, cudaMemcpyHostToDevice, st));
+  CU_OK(cudaMemcpyAsync(l->lcnts, lcnts, (size_t)l->G * 4, cudaMemcpyHostToDevice, st));
+  CU_OK(cudaStreamSynchronize(st));
+  l->have_placement = true;
+  return 0;
+}
+
+extern "C" int zepp_layer_set_weights(zepp_layer* l, const void* w1, const void* w2) {
+  if (make_map(&l->tm_w1, w1, (uint64_t)l->gpe * l->ffn1, l->H, 128)) return 1;
+  if (make_map(&l->tm_w2, w2, (uint64_t)l->gpe * l->H, l->I, 128)) return 1;
+  l->have_weights = true;
+  return 0;
+}
+
+#define LAUNCH_OK()                                                                          \
+  do {                                                                                       \
+    cudaError_t _e = cudaGetLastError();                                                     \
+    if (_e != cudaSuccess) return fail("kernel launch failed: %s (%s:%d)", cudaGetErrorString(_e), __FILE__, __LINE__); \
+    l->launches++;                                                                           \
+  } while (0)
+
+static MetaArgs layer_meta_args(zepp_layer* l) {
+  MetaArgs m{};
+  const int b = (int)(l->epoch & 1);
+  m.gathered = l->xchg_all[b];
+  m.vce_in = nullptr;
+  m.R = l->W; m.L = l->L; m.S = l->S; m.K = l->K; m.nlp = l->nlp; m.gpe = l->gpe; m.my_rank = l->rt->rank;
+  m.tokens_per_tile = l->tokens_per_tile; m.tiles_per_src = l->tiles_per_src;
+  m.vce = l->vce; m.probs_all = l->probs_all; m.splits = l->splits; m.scatter_index = l->scatter_index;
+  m.sps = l->sps; m.uc = l->uc; m.demands = l->demands;
+  for (int i = 0; i < 8; ++i) m.caps[i] = l->cfg.caps[i];
+  m.direct = l->cfg.strategy == 1; m.relay_slots = 2;
+  m.dplan = l->dplan; m.cplan = l->NN == 1 ? l->cplan : nullptr; m.copies_per_rank = l->SK;
+  m.tile_hist = l->tile_hist; m.tile_uc = l->tile_uc; m.expert_base = l->expert_base;
+  m.n_tiles = l->n_tiles; m.tile_group = l->tile_group; m.tile_row0 = l->tile_row0; m.tile_rows = l->tile_rows;
+  m.tile_ready = l->tile_ready; m.max_tiles = l->max_tiles; m.recv_cap = l->cap; m.m_this = l->m_this;
+  m.row_tok = l->row_tok; m.row_dst = l->row_dst; m.row_scale = l->row_scale; m.hidden = l->H;
+  m.group_order = nullptr;
+  m.routing_flags = l->W > 1 ? l->routing_flags : nullptr;
+  m.epoch = l->epoch; m.limit_ns = l->rt->wait_ns; m.status = l->status;
+  return m;
+}
+
+static size_t meta_smem(int R, int NN, int E_virt) { return (size_t)(E_virt + R + NN) * sizeof(int); }
+
+extern "C" int zepp_layer_prepare_phase(zepp_layer* l, int phase, const int32_t* ids, const float* wts, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  CU_OK(cudaSetDevice(l->rt->device));
+  if (!l->have_placement) return fail("prepare: no placement set");
+  const int R = l->W, me = l->rt->rank;
+  if (phase == 0) {
+    l->epoch += 1;
+    const int b = (int)(l->epoch & 1);
+    CU_OK(cudaMemcpyAsync(l->topk_own, ids, (size_t)l->SK * 4, cudaMemcpyDeviceToDevice, st));
+    CU_OK(cudaMemcpyAsync(l->probs_own, wts, (size_t)l->SK * 4, cudaMemcpyDeviceToDevice, st));
+    loads_publish_kernel<<<1, 1024, l->G * sizeof(int), st>>>(l->topk_own, l->SK, l->G, me, R, l->loads_dst[b],
+                                                             l->loads_flag_dst, l->epoch, l->status);
+    LAUNCH_OK();
+    return 0;
+  }
+  const int b = (int)(l->epoch & 1);
+  if (phase == 1) {
+    RouteArgs ra{};
+    ra.topk_own = l->topk_own; ra.n_entries = l->SK; ra.loads = l->loads_all[b]; ra.l2p = l->l2p; ra.lcnts = l->lcnts;
+    ra.G = l->G; ra.R = R; ra.L = l->L; ra.nlp = l->nlp; ra.my_rank = me;
+    ra.c_num = l->cfg.c_num; ra.c_den = l->cfg.c_den; ra.ws = l->route_ws; ra.phys_own = l->phys_own;
+    ra.loads_flags = R > 1 ? l->loads_flags : nullptr;
+    ra.epoch = l->epoch; ra.limit_ns = l->rt->wait_ns; ra.status = l->status; ra.stats = l->route_stats;
+    CU_OK(cudaMemsetAsync(l->route_stats, 0, 32, st));
+    route_kernel<<<(l->G + 7) / 8, 256, 0, st>>>(ra);
+    LAUNCH_OK();
+    if (l->cfg.swap) {
+      // decision + lane metadata on scratch copies of the tables (the decision is reported in the
+      // result block; the resident placement changes only through zepp_layer_set_placement)
+      CU_OK(cudaMemcpyAsync(l->p2l_try, l->p2l, (size_t)R * l->nlp * 4, cudaMemcpyDeviceToDevice, st));
+      CU_OK(cudaMemcpyAsync(l->l2p_try, l->l2p, (size_t)l->G * R * 4, cudaMemcpyDeviceToDevice, st));
+      const double C = (double)l->cfg.c_num / (double)l->cfg.c_den;
+      if (zepp_swap_decide(l->loads_all[b], l->p2l_try, l->l2p_try, l->lcnts, R, l->G, l->L, l->nlp, C, 8, 32,
+                           (int64_t*)l->swap_block, stream))
+        return 1;
+      l->launches++;
+      CU_OK(cudaMemsetAsync(l->sched, 0, l->gpe * 4, st));
+      if (zepp_lane_arm((const int64_t*)l->swap_block, R, me, l->nlp, 8, (int64_t*)l->gate, l->sched,
+                        (int64_t*)l->ovr0, (int64_t*)l->ovr1, (const int64_t*)l->stag, (int64_t)l->epoch, stream))
+        return 1;
+      l->launches++;
+    }
+    FinishArgs fa{};
+    fa.topk_own = l->topk_own; fa.phys_own = l->phys_own; fa.probs_own = l->probs_own;
+    fa.S = l->S; fa.K = l->K; fa.G = l->G; fa.R = R; fa.L = l->L; fa.nlp = l->nlp; fa.my_rank = me;
+    fa.ws = l->route_ws; fa.send_row = l->send_row; fa.dst = l->xchg_dst[b]; fa.flags = l->routing_flag_dst;
+    fa.world = R; fa.epoch = l->epoch; fa.block_counter = l->counters + 0; fa.status = l->status;
+    fa.stats = l->route_stats;
+    if (l->NN > 1) {
+      route_vacate_kernel<<<1, 32, 0, st>>>(fa);
+      LAUNCH_OK();
+    }
+    route_finish_kernel<<<8, 256, 0, st>>>(fa);
+    LAUNCH_OK();
+    return 0;
+  }
+  if (phase == 2) {
+    MetaArgs m = layer_meta_args(l);
+    const int grid = R * l->tiles_per_src;
+    const size_t sm = meta_smem(R, l->NN, l->E_virt);
+    meta_pass1_kernel<<<grid, kMetaThreads, sm, st>>>(m);
+    LAUNCH_OK();
+    meta_scan_kernel<<<1, kMetaThreads, 0, st>>>(m);
+    LAUNCH_OK();
+    meta_pass2_kernel<<<grid, kMetaThreads, sm, st>>>(m);
+    LAUNCH_OK();
+    return 0;
+  }
+  return fail("prepare: bad phase %d", phase);
+}
+
+extern "C" int zepp_layer_prepare(zepp_layer* l, const int32_t* ids, const float* wts, void* stream) {
+  for (int ph = 0; ph < 3; ++ph)
+    if (zepp_layer_prepare_phase(l, ph, ids, wts, stream)) return 1;
+  return 0;
+}
+
+static GemmArgs layer_gemm_args(zepp_layer* l, bool first) {
+  GemmArgs g{};
+  g.tt.n_tiles = l->n_tiles; g.tt.tile_group = l->tile_group; g.tt.tile_row0 = l->tile_row0; g.tt.tile_rows = l->tile_rows;
+  g.k_extent = first ? l->H : l->I;
+  g.n_feat_tiles = first ? l->I / kTileM : l->H / kTileM;
+  g.w_rows_per_group = first ? l->ffn1 : l->H;
+  g.up_row_offset = l->I;
+  g.act = l->act; g.ld_act = l->I;
+  g.row_scale = l->row_scale; g.row_dst = l->row_dst; g.panels = l->panels; g.staging = nullptr;
+  g.done_flags = nullptr; g.cta_counter = l->counters + 2;
+  g.world = l->W; g.rank = l->rt->rank; g.epoch = l->epoch;
+  g.row_tok = l->row_tok; g.x_ptrs = l->x_ptrs[l->epoch & 1]; g.x_self = (const __nv_bfloat16*)l->x_self;
+  g.x_flags = l->W > 1 ? l->x_flags : nullptr;
+  g.recv = l->recv; g.tile_ready = l->tile_ready; g.tokens_per_rank = l->S; g.gather = 0;
+  g.status = l->status; g.mbar_limit = 1u << 24; g.flag_limit_ns = l->rt->wait_ns;
+  return g;
+}
+
+template <int MODE>
+static int launch_gemm(zepp_layer* l, const CUtensorMap& tw, const CUtensorMap* tx, GemmArgs& g, cudaStream_t st) {
+  const int threads = g.gather ? 320 : 192;
+  const int grid = l->rt->sm_count;
+  const size_t smem = GemmCfg<MODE>::kSmemBytes;
+  if (g.gather) {
+    // gather warps of one CTA feed the producers of others: every CTA must be resident
+    void* args[] = {(void*)&tw, (void*)&tx[0], (void*)&tx[1], (void*)&tx[2], (void*)&g};
+    CU_OK(cudaLaunchCooperativeKernel((const void*)moe_gemm_kernel<MODE>, dim3(grid), dim3(threads), args, smem, st));
+    l->launches++;
+    return 0;
+  }
+  moe_gemm_kernel<MODE><<<grid, threads, smem, st>>>(tw, tx[0], tx[1], tx[2], g);
+  LAUNCH_OK();
+  return 0;
+}
+
+static MoveArgs layer_move_args(zepp_layer* l) {
+  MoveArgs m{};
+  m.m_this = l->m_this; m.row_tok = l->row_tok; m.row_dst = l->row_dst;
+  m.x_ptrs = l->x_ptrs[l->epoch & 1]; m.x_self = (const __nv_bfloat16*)l->x_self;
+  m.recv = l->recv; m.staging = l->staging; m.panels = l->panels; m.done_flags = l->done_ptrs;
+  m.x_flags = l->W > 1 ? l->x_flags : nullptr; m.counter = l->counters + 4;
+  m.H = l->H; m.S = l->S; m.world = l->W; m.rank = l->rt->rank; m.recv_cap = l->cap;
+  m.epoch = l->epoch; m.limit_ns = l->rt->wait_ns; m.status = l->status;
+  return m;
+}
+
+extern "C" int zepp_layer_forward_phase(zepp_layer* l, int phase, const void* x, void* y, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  CU_OK(cudaSetDevice(l->rt->device));
+  if (!l->have_weights) return fail("forward: no weights set");
+  if (l->epoch == 0) return fail("forward: prepare has not run");
+  const bool direct = l->cfg.strategy == 1;
+  const int b = (int)(l->epoch & 1);
+  if (phase == 0) {
+    l->x_self = x;
+    if (l->W > 1) {
+      const size_t n_vec = (size_t)l->S * l->H / 8;
+      publish_x_kernel<<<64, 256, 0, st>>>((const uint4*)x, (uint4*)l->xsym[b], n_vec, l->rt->rank, l->W,
+                                          l->x_flag_dst, l->epoch, l->counters + 6);
+      LAUNCH_OK();
+    }
+    return 0;
+  }
+  if (phase == 1) {
+    l->x_self = x;
+    GemmArgs g = layer_gemm_args(l, true);
+    if (direct) {
+      MoveArgs m = layer_move_args(l);
+      dispatch_pull_kernel<<<l->rt->sm_count * 2, 256, 0, st>>>(m);
+      LAUNCH_OK();
+    } else {
+      g.gather = 1;
+    }
+    if (l->cfg.act == 1) return launch_gemm<MODE_GATE_UP_SWIGLU>(l, l->tm_w1, l->tm_recv, g, st);
+    return launch_gemm<MODE_SINGLE_GELU>(l, l->tm_w1, l->tm_recv, g, st);
+  }
+  if (phase == 2) {
+    GemmArgs g = layer_gemm_args(l, false);
+    if (direct) {
+      g.staging = l->staging;
+    } else {
+      g.done_flags = l->done_ptrs;
+    }
+    if (launch_gemm<MODE_DOWN_COMBINE>(l, l->tm_w2, l->tm_act, g, st)) return 1;
+    if (direct) {
+      MoveArgs m = layer_move_args(l);
+      combine_push_kernel<<<l->rt->sm_count * 2, 256, 0, st>>>(m);
+      LAUNCH_OK();
+    }
+    return 0;
+  }
+  if (phase == 3) {
+    combine_reduce_kernel<<<l->rt->sm_count * 2, 256, 0, st>>>(l->panel, (__nv_bfloat16*)y, l->S, l->K, l->H,
+                                                            l->done_flags, l->W, l->epoch, l->rt->wait_ns, l->status);
+    LAUNCH_OK();
+    return 0;
+  }
+  return fail("forward: bad phase %d", phase);
+}
+
+extern "C" int zepp_layer_forward(zepp_layer* l, const void* x, void* y, void* stream) {
+  for (int ph = 0; ph < 4; ++ph)
+    if (zepp_layer_forward_phase(l, ph, x, y, stream)) return 1;
+  return 0;
+}
+
+extern "C" int zepp_layer_status(zepp_layer* l, void* stream, uint64_t out[8]) {
+  cudaStream_t st = (cudaStream_t)stream;
+  CU_OK(cudaSetDevice(l->rt->device));
+  CU_OK(cudaStreamSynchronize(st));
+  CU_OK(cudaMemcpy(out, l->status, ST_WORDS * 8, cudaMemcpyDeviceToHost));
+  CU_OK(cudaMemset(l->status, 0, 4 * 8));
+  return 0;
+}
+
+extern "C" int zepp_layer_gpu_launches(zepp_layer* l, int64_t* out) {
+  *out = l->launches;
+  return 0;
+}
+
+extern "C" int zepp_layer_table(zepp_layer* l, int which, void** p, size_t* bytes) {
+  const size_t R = l->W, SK = l->SK;
+  const int b = (int)(l->epoch & 1);
+  switch (which) {
+    case ZEPP_T_LOADS: *p = l->loads_all[b]; *bytes = R * l->G * 4; break;
+    case ZEPP_T_PHYS_OWN: *p = l->phys_own; *bytes = SK * 4; break;
+    case ZEPP_T_VCE: *p = l->vce; *bytes = R * SK * 4; break;
+    case ZEPP_T_PROBS_ALL: *p = l->probs_all; *bytes = R * SK * 4; break;
+    case ZEPP_T_SPLITS: *p = l->splits; *bytes = (size_t)l->E_virt * 4; break;
+    case ZEPP_T_SCATTER_INDEX: *p = l->scatter_index; *bytes = R * SK * 4; break;
+    case ZEPP_T_SPS: *p = l->sps; *bytes = R * l->E_virt * 4; break;
+    case ZEPP_T_UC: *p = l->uc; *bytes = R * (R + l->NN) * 4; break;
+    case ZEPP_T_DEMANDS: *p = l->demands; *bytes = 64; break;
+    case ZEPP_T_DPLAN: *p = l->dplan; *bytes = (size_t)zepp_dispatch_plan_words(l->L, l->NN) * 8; break;
+    case ZEPP_T_CPLAN: *p = l->cplan; *bytes = (4 * R + 2) * 8; break;
+    case ZEPP_T_ROUTE_WS: *p = l->route_ws; *bytes = (size_t)zepp_route_workspace_ints(l->G, l->W) * 4; break;
+    case ZEPP_T_SWAP_BLOCK: *p = l->swap_block; *bytes = (size_t)zepp_swap_decide_out_ints(l->W, l->G, l->nlp, 8) * 8; break;
+    case ZEPP_T_M_THIS: *p = l->m_this; *bytes = 8; break;
+    case ZEPP_T_ROW_TOK: *p = l->row_tok; *bytes = (size_t)l->cap * 4; break;
+    case ZEPP_T_ACT: *p = l->act; *bytes = (size_t)l->cap * l->I * 2; break;
+    case ZEPP_T_RECV: *p = l->recv; *bytes = (size_t)l->cap * l->H * 2; break;
+    case ZEPP_T_P2L: *p = l->p2l; *bytes = R * l->nlp * 4; break;
+    case ZEPP_T_L2P: *p = l->l2p; *bytes = (size_t)l->G * R * 4; break;
+    case ZEPP_T_N_TILES: *p = l->n_tiles; *bytes = 4; break;
+    case ZEPP_T_PANEL: *p = l->panel; *bytes = SK * l->H * 2; break;
+    case ZEPP_T_GATE: *p = l->gate; *bytes = (size_t)2 * l->gpe * 8; break;
+    case ZEPP_T_SCHED: *p = l->sched; *bytes = (size_t)l->gpe * 4; break;
+    default: return fail("layer_table: unknown table %d", which);
+  }
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// stand-alone planner entry points
+// ---------------------------------------------------------------------------------------------
+extern "C" int zepp_route_workspace_ints(int G, int R) { return route_ws_layout(G, R).total; }
+
+extern "C" int zepp_route_ws_offsets(int G, int R, int64_t o[10]) {
+  const RouteWs w = route_ws_layout(G, R);
+  o[0] = w.rep; o[1] = w.rphys; o[2] = w.c; o[3] = w.D; o[4] = w.U; o[5] = w.Lb; o[6] = w.fill; o[7] = w.M;
+  o[8] = w.rel; o[9] = w.ext;
+  return 0;
+}
+
+extern "C" int zepp_route(const int32_t* topk_own, int S, int K, const int32_t* loads, const int32_t* l2p,
+                          const int32_t* lcnts, int G, int R, int my_rank, int nlp, int L, int64_t c_num, int64_t c_den,
+                          int32_t* ws, const float* probs_own, int32_t* send_row, int32_t* phys_own, int64_t* stats,
+                          void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (R < 1 || R > kMaxRanks || L < 1 || R % L) return fail("route: bad topology R=%d L=%d", R, L);
+  if (K > 64) return fail("route: topk > 64");
+  RouteArgs ra{};
+  ra.topk_own = topk_own; ra.n_entries = S * K; ra.loads = loads; ra.l2p = l2p; ra.lcnts = lcnts;
+  ra.G = G; ra.R = R; ra.L = L; ra.nlp = nlp; ra.my_rank = my_rank; ra.c_num = c_num; ra.c_den = c_den;
+  ra.ws = ws; ra.phys_own = phys_own; ra.loads_flags = nullptr; ra.epoch = 0; ra.limit_ns = 0; ra.status = nullptr;
+  ra.stats = (long long*)stats;
+  if (stats) CU_OK(cudaMemsetAsync(stats, 0, 32, st));
+  route_kernel<<<(G + 7) / 8, 256, 0, st>>>(ra);
+  CU_OK(cudaGetLastError());
+  FinishArgs fa{};
+  fa.topk_own = topk_own; fa.phys_own = phys_own; fa.probs_own = probs_own; fa.S = S; fa.K = K; fa.G = G; fa.R = R;
+  fa.L = L; fa.nlp = nlp; fa.my_rank = my_rank; fa.ws = ws; fa.send_row = send_row; fa.world = 0; fa.epoch = 0;
+  fa.status = nullptr; fa.stats = (long long*)stats;
+  if (R / L > 1 && topk_own != nullptr) {
+    route_vacate_kernel<<<1, 32, 0, st>>>(fa);
+    CU_OK(cudaGetLastError());
+  }
+  if (send_row != nullptr && probs_own != nullptr) {
+    static unsigned int* counter = nullptr;      // one word, lives for the process
+    if (!counter) {
+      CU_OK(cudaMalloc(&counter, 64));
+      CU_OK(cudaMemset(counter, 0, 64));
+    }
+    fa.block_counter = counter;
+    route_finish_kernel<<<1, 256, 0, st>>>(fa);
+    CU_OK(cudaGetLastError());
+  }
+  return 0;
+}
+
+extern "C" size_t zepp_meta_workspace_bytes(int R, int S, int K, int gpe) {
+  const int tpt = kMetaThreads / K;
+  const size_t tiles = (size_t)R * ((S + tpt - 1) / tpt);
+  const size_t E = (size_t)R * gpe;
+  return al(tiles * E * 4) + al(tiles * 2 * R * 4) + al((E + 1) * 4) + 4096;
+}
+
+extern "C" int zepp_dispatch_plan_words(int L, int NN) {
+  const int nseg = L + NN - 1;
+  return 8 + nseg + 1 + 3 * L + NN * (6 + 8 * L) + NN * (3 + L);
+}
+
+extern "C" int zepp_routed_meta(const int32_t* gathered, const int32_t* vce_in, int R, int L, int S, int K, int nlp,
+                                int gpe, int my_rank, int direct, int relay_slots, const int64_t caps[8],
+                                int copies_per_rank, int32_t* vce, float* probs_all, int32_t* splits,
+                                int32_t* scatter_index, int32_t* sps, int32_t* uc, int64_t* demands, int64_t* dplan,
+                                int64_t* cplan, void* ws, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (R < 1 || R > kMaxRanks || R % L) return fail("routed_meta: bad topology");
+  if (K < 1 || K > 64) return fail("routed_meta: bad topk");
+  const int E_virt = R * gpe, NN = R / L;
+  if (E_virt > 4 * kMetaThreads) return fail("routed_meta: too many virtual experts");
+  if (gathered && !probs_all) return fail("routed_meta: probs_all is required with gathered rows");
+  MetaArgs m{};
+  m.gathered = gathered; m.vce_in = vce_in; m.R = R; m.L = L; m.S = S; m.K = K; m.nlp = nlp; m.gpe = gpe;
+  m.my_rank = my_rank;
+  m.tokens_per_tile = kMetaThreads / K;
+  m.tiles_per_src = (S + m.tokens_per_tile - 1) / m.tokens_per_tile;
+  m.vce = vce; m.probs_all = probs_all; m.splits = splits; m.scatter_index = scatter_index; m.sps = sps; m.uc = uc;
+  m.demands = (long long*)demands;
+  for (int i = 0; i < 8; ++i) m.caps[i] = caps[i];
+  m.direct = direct; m.relay_slots = relay_slots; m.dplan = (long long*)dplan; m.cplan = (long long*)cplan;
+  m.copies_per_rank = copies_per_rank;
+  uint8_t* w = (uint8_t*)ws;
+  const size_t tiles = (size_t)R * m.tiles_per_src;
+  m.tile_hist = (int*)w; w += al(tiles * E_virt * 4);
+  m.tile_uc = (int*)w; w += al(tiles * 2 * R * 4);
+  m.expert_base = (int*)w;
+  m.n_tiles = nullptr; m.row_tok = nullptr; m.status = nullptr; m.routing_flags = nullptr;
+  const int grid = (int)tiles;
+  const size_t sm = meta_smem(R, NN, E_virt);
+  meta_pass1_kernel<<<grid, kMetaThreads, sm, st>>>(m);
+  CU_OK(cudaGetLastError());
+  meta_scan_kernel<<<1, kMetaThreads, 0, st>>>(m);
+  CU_OK(cudaGetLastError());
+  meta_pass2_kernel<<<grid, kMetaThreads, sm, st>>>(m);
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int zepp_swap_decide_out_ints(int R, int G, int nlp, int cap) { return 3 + R + 4 * R * cap + R * nlp + G; }
+
+extern "C" int zepp_swap_decide(const int32_t* loads, int32_t* p2l, int32_t* l2p, const int32_t* lcnts, int R, int G,
+                                int L, int nlp, double C, int cap, int max_rounds, int64_t* out, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (R % L || L > kSwapMaxL) return fail("swap_decide: bad topology R=%d L=%d", R, L);
+  SwapArgs a{};
+  a.loads = loads; a.p2l = p2l; a.l2p = l2p; a.lcnts = lcnts; a.R = R; a.G = G; a.L = L; a.nlp = nlp; a.cap = cap;
+  a.max_rounds = max_rounds; a.C = C; a.out = (long long*)out;
+  const int NS = R * nlp, NN = R / L, Q = NN * (L / 2) > 0 ? NN * (L / 2) : 1;
+  const size_t sm = (size_t)(G + NS + R) * 8 + (size_t)(2 * NS + 7 * Q + NN + (kSwapThreads / 32) * 16 + 8) * 4;
+  if (sm > 200 * 1024) return fail("swap_decide: tables too large for one block");
+  static bool attr = false;
+  if (!attr) {
+    CU_OK(cudaFuncSetAttribute(swap_decide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    attr = true;
+  }
+  swap_decide_kernel<<<1, kSwapThreads, sm, st>>>(a);
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int zepp_lane_arm(const int64_t* swap_out, int R, int rank, int nlp, int cap, int64_t* gate, int32_t* sched,
+                             int64_t* ovr0, int64_t* ovr1, const int64_t* stag, int64_t epoch, void* stream) {
+  lane_arm_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((const long long*)swap_out, R, rank, nlp, cap, (long long*)gate,
+                                                      sched, (long long*)ovr0, (long long*)ovr1,
+                                                      (const long long*)stag, (long long)epoch);
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+
+__global__ void wait_geq_kernel(const unsigned long long* flag, unsigned long long value, unsigned long long limit_ns,
+                                int* result) {
+  if (threadIdx.x == 0) result[0] = wait_epoch_geq(flag, value, limit_ns) ? 1 : 0;
+}
+
+extern "C" int zepp_wait_geq(const uint64_t* flag, uint64_t value, int limit_ms, int32_t* result, void* stream) {
+  if (limit_ms < 1 || limit_ms > 10000) return fail("wait_geq: limit must be 1..10000 ms");
+  wait_geq_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((const unsigned long long*)flag, value,
+                                                      (unsigned long long)limit_ms * 1000000ull, result);
+  CU_OK(cudaGetLastError());
+  return 0;
+}

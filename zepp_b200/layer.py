@@ -1,0 +1,255 @@
+"""EPMoE: the expert-parallel MoE layer behind the reference's Python API
+(python/zepp/layer.py:36-225):
+
+    layer = EPMoE(cfg, group, sizing_routing=..., pool_routing=...)   # collective
+    layer.load_weights(w1_of, w2_of)          # expert -> [ffn1, H] / [H, ffn]
+    layer.prime(topk_ids, topk_weights)
+    plan = layer.prepare(topk_ids, topk_weights)    # loads, (swap decision), route, metadata
+    y = layer.forward(x, plan)                      # dispatch_gemm -> activation -> gemm_combine
+
+Everything per step runs on the GPU through libzepp_b200.so: planning is integer CUDA kernels,
+the two grouped GEMMs are tcgen05 kernels with the token transfers inside them (overlap) or beside
+them (direct), and nothing is read back on the host inside a step.  Unlike the reference, whose
+device planning needs two or more nodes (python/zepp/layer.py:66), device planning is always on.
+"""
+import torch
+
+from . import constants
+from .capacity import CapacityExceeded, Demands, violations
+from .config import EPMoEConfig
+from .placement import Placement, demand_histogram, solve_placement
+from .planner import Plan
+from .routing import c_rational, compute_capacities
+from .runtime import LayerHandle, Runtime, make_cfg
+from .swap import swap_orbit
+
+
+def activation(h, shape, out=None):
+    """The expert activation between the GEMMs as a torch op (the fused kernels apply the same
+    function in their epilogue; python/zepp/layer.py:20-27)."""
+    if shape.act == "gelu":
+        return torch.nn.functional.gelu(h)
+    ffn = shape.ffn_hidden
+    return torch.mul(torch.nn.functional.silu(h[:, :ffn]), h[:, ffn:], out=out)
+
+
+class Marks:
+    """Optional bracket marks for benchmarking (a callable per boundary)."""
+
+    def __call__(self, name):
+        pass
+
+
+class LocalGroup:
+    """Stand-in for a process group when all ranks live in this process (single-GPU emulation)."""
+    is_local = True
+
+    def __init__(self, rank, world):
+        self._rank, self._world = rank, world
+
+    def rank(self):
+        return self._rank
+
+    def size(self):
+        return self._world
+
+
+_ERR_NAMES = {1: "a device-side wait ran out", 2: "the step exceeded the buffer capacities",
+              4: "an index table entry was out of range", 8: "the router could not place all rows"}
+
+
+class EPMoE(torch.nn.Module):
+    def __init__(self, cfg: EPMoEConfig, group, sizing_routing, pool_routing, probs_own=None,
+                 dtype=torch.bfloat16, _runtime=None):
+        """sizing_routing [R, S, K]: expert ids of a representative batch (sizes the buffers from the
+        provable routing bounds); pool_routing [R, S', K]: ids the placement is planned from;
+        probs_own is accepted for signature compatibility (gate weights are set by prepare)."""
+        super().__init__()
+        assert dtype == torch.bfloat16, "the B200 kernels compute in bf16 with fp32 accumulation"
+        self.cfg, self.group, self.dtype = cfg, group, dtype
+        self.rank = group.rank()
+        shape = cfg.shape
+        R, L, nlp = cfg.ranks, cfg.ranks_per_node, cfg.slots_per_rank
+        assert group.size() == R
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        hist = demand_histogram(pool_routing.to(self.device), L, shape.num_experts).cpu()
+        self.placement = solve_placement(hist, L, nlp)
+        sizing_cpu = sizing_routing.cpu()
+        placements = [self.placement]
+        if cfg.swap:
+            load_g = torch.bincount(sizing_cpu.reshape(-1).long(), minlength=shape.num_experts)
+            placements += swap_orbit(load_g, self.placement, L, nlp, cfg.router_c, device=self.device)
+        self.caps = compute_capacities(sizing_cpu, placements, nlp, L, cfg.router_c, group, device=self.device)
+        self.redos = 0
+        self.gpu_plan = True
+        self.c_num, self.c_den = c_rational(cfg.router_c)
+        self._ccfg = make_cfg(cfg, self.caps, self.c_num, self.c_den)
+        if _runtime is None:
+            self._rt = Runtime(self.rank, R, self.device.index, LayerHandle.arena_bytes(self._ccfg))
+            if R > 1:
+                self._rt.exchange_handles(group)
+            self._own_rt = True
+        else:
+            self._rt, self._own_rt = _runtime, False
+        self._h = LayerHandle(self._rt, self._ccfg)
+        self._h.set_placement(self.placement)
+        self.w1 = self.w2 = None
+        self._y = torch.empty(cfg.max_tokens_per_rank, shape.hidden, dtype=dtype, device=self.device)
+        self._swap_moves = 0
+        self._epoch = 0
+        self._plan_views = None
+
+    @staticmethod
+    def arena_bytes(cfg, caps):
+        c_num, c_den = c_rational(cfg.router_c)
+        return LayerHandle.arena_bytes(make_cfg(cfg, caps, c_num, c_den))
+
+    # -- weights ------------------------------------------------------------------------
+    def load_weights(self, w1_of, w2_of):
+        """w1_of(e) -> [ffn1, H], w2_of(e) -> [H, ffn] for every expert this rank hosts; the pad group
+        and unassigned redundant slots stay zero."""
+        cfg, shape = self.cfg, self.cfg.shape
+        nlp, gpe = cfg.slots_per_rank, cfg.groups_per_rank
+        w1 = torch.zeros(gpe, shape.ffn1, shape.hidden, dtype=self.dtype, device=self.device)
+        w2 = torch.zeros(gpe, shape.hidden, shape.ffn_hidden, dtype=self.dtype, device=self.device)
+        for i in range(nlp):
+            e = int(self.placement.p2l[self.rank * nlp + i])
+            if e < 0:
+                continue
+            w1[1 + i].copy_(w1_of(e).to(self.dtype))
+            w2[1 + i].copy_(w2_of(e).to(self.dtype))
+        self.set_weights(w1, w2)
+
+    def set_weights(self, w1_slots, w2_slots):
+        """Per-group weights [gpe, ffn1, H] / [gpe, H, ffn]; the layer keeps references (no copy)."""
+        shape, gpe = self.cfg.shape, self.cfg.groups_per_rank
+        assert w1_slots.shape == (gpe, shape.ffn1, shape.hidden), tuple(w1_slots.shape)
+        assert w2_slots.shape == (gpe, shape.hidden, shape.ffn_hidden), tuple(w2_slots.shape)
+        self.w1, self.w2 = w1_slots.contiguous(), w2_slots.contiguous()
+        self._h.set_weights(self.w1, self.w2)
+
+    # -- setup ------------------------------------------------------------------------
+    def prime(self, topk_ids, topk_weights):
+        """One planning pass with every rank quiesced (loads kernels, checks the routing)."""
+        plan = self.prepare(topk_ids, topk_weights)
+        self.check()
+        self._barrier()
+        return plan
+
+    def _barrier(self):
+        torch.cuda.synchronize()
+        if self.cfg.ranks > 1 and not getattr(self.group, "is_local", False):
+            torch.distributed.barrier(group=self.group)
+
+    # -- per iteration ----------------------------------------------------------------------
+    def _ids(self, topk_ids, topk_weights):
+        ids = topk_ids.to(device=self.device, dtype=torch.int32).contiguous()
+        wts = topk_weights.to(device=self.device, dtype=torch.float32).contiguous()
+        assert ids.shape == (self.cfg.max_tokens_per_rank, self.cfg.shape.topk), tuple(ids.shape)
+        return ids, wts
+
+    def prepare(self, topk_ids, topk_weights, marks=Marks(), phase=None):
+        """Loads exchange -> (swap decision) -> route -> routing exchange -> metadata; returns the Plan.
+        `phase` (0, 1, 2) runs one stage only: ranks emulated inside one process advance in lock step."""
+        ids, wts = self._ids(topk_ids, topk_weights)
+        if phase is None:
+            self._h.prepare(ids, wts, 0)
+            marks("plan_comm")
+            self._h.prepare(ids, wts, 1)
+            marks("place")
+            self._h.prepare(ids, wts, 2)
+            marks("plan")
+        else:
+            self._h.prepare(ids, wts, phase)
+            if phase < 2:
+                return None
+        self._epoch += 1
+        if self._plan_views is None:          # runtime buffers: the addresses never change
+            K = self.cfg.shape.topk
+            self._plan_views = (self._h.table("vce").view(-1, K), self._h.table("probs_all").view(-1, K))
+        return Plan(self._plan_views[0], self._plan_views[1], stable=True, epoch=self._epoch)
+
+    def forward(self, x, plan=None, marks=Marks(), phase=None):
+        assert x.shape == (self.cfg.max_tokens_per_rank, self.cfg.shape.hidden), tuple(x.shape)
+        x = x.contiguous()
+        if phase is not None:
+            self._h.forward(x, self._y, phase)
+            return self._y
+        self._h.forward(x, self._y, 0)
+        self._h.forward(x, self._y, 1)
+        marks("dispatch")
+        marks("act")                     # the activation runs in the dispatch GEMM's epilogue
+        self._h.forward(x, self._y, 2)
+        self._h.forward(x, self._y, 3)
+        marks("combine")
+        return self._y
+
+    # -- verdict ----------------------------------------------------------------------------
+    def check(self):
+        """Synchronise and raise if the last steps recorded a device-side error (a wait that ran out,
+        a capacity violation, a bad index).  The reference checks capacities on the host before it
+        launches (python/zepp/comm/overlap.py:136-145); here the verdict is deferred and read on demand."""
+        st = self._h.status()
+        if st[4]:
+            dem = self._h.table("demands").cpu().tolist()
+            d = Demands(*[int(v) for v in dem[:7]])
+            raise CapacityExceeded(violations(d, self.caps, direct=self.cfg.comm_strategy == "direct"), d)
+        if st[0]:
+            what = ", ".join(n for b, n in _ERR_NAMES.items() if st[0] & b)
+            raise RuntimeError(f"zepp_b200 step failed: {what} (wait id {st[1]}, peer/item {st[2]}, epoch {st[3]})")
+
+    def tables(self, *names):
+        """Planner products of the last prepare (device tensors): see runtime.TABLES."""
+        return [self._h.table(n) for n in names]
+
+    @property
+    def gpu_launches(self):
+        return self._h.launches()
+
+    @property
+    def swap_moves(self):
+        return self._swap_moves
+
+    def prep(self):
+        """Per-iteration hygiene hook of the reference's benchmark loop: nothing to clear here (every
+        buffer row that is read in a step is written in that step)."""
+        return
+
+    def close(self):
+        self._h.destroy()
+        if self._own_rt:
+            self._rt.destroy()
+
+
+def make_local_layers(cfg: EPMoEConfig, sizing_routing, pool_routing, wait_limit_ms=None):
+    """All `cfg.ranks` ranks of a layer inside this process on the current GPU (their arenas are
+    linked by plain pointers).  Kernels of different ranks never wait on one another this way as
+    long as every rank finishes a phase before any rank starts the next: use `local_step`."""
+    R = cfg.ranks
+    dev = torch.device("cuda", torch.cuda.current_device())
+    hist = demand_histogram(pool_routing.to(dev), cfg.ranks_per_node, cfg.shape.num_experts).cpu()
+    pl = solve_placement(hist, cfg.ranks_per_node, cfg.slots_per_rank)
+    placements = [pl]
+    if cfg.swap:
+        load_g = torch.bincount(sizing_routing.reshape(-1).long(), minlength=cfg.shape.num_experts)
+        placements += swap_orbit(load_g, pl, cfg.ranks_per_node, cfg.slots_per_rank, cfg.router_c, device=dev)
+    caps = compute_capacities(sizing_routing.cpu(), placements, cfg.slots_per_rank, cfg.ranks_per_node, cfg.router_c,
+                              None, device=dev)
+    nbytes = EPMoE.arena_bytes(cfg, caps)
+    rts = [Runtime(r, R, dev.index, nbytes) for r in range(R)]
+    if wait_limit_ms:
+        for rt in rts:
+            rt.set_wait_limit_ms(wait_limit_ms)
+    Runtime.link_local(rts)
+    return [EPMoE(cfg, LocalGroup(r, R), sizing_routing, pool_routing, _runtime=rts[r]) for r in range(R)], rts
+
+
+def local_step(layers, ids_all, wts_all, xs):
+    """One layer step of in-process ranks, phase by phase; returns the list of outputs."""
+    for ph in range(3):
+        for r, l in enumerate(layers):
+            l.prepare(ids_all[r], wts_all[r], phase=ph)
+    for ph in range(4):
+        for r, l in enumerate(layers):
+            l.forward(xs[r], phase=ph)
+    return [l._y for l in layers]
