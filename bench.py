@@ -15,7 +15,6 @@ import argparse
 import json
 import os
 import statistics
-import subprocess
 import sys
 import threading
 import time
@@ -51,41 +50,56 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
-    Q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
-        "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+    """Samples SM clocks and throttle reasons of one GPU through NVML (read-only) from a thread while
+    the timed region runs."""
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
-    def __init__(self, index):
-        self.index, self.rows, self.proc = index, [], None
+    def __init__(self, index, period_s=0.002):
+        self.index, self.period, self.sm, self.bits, self.max_mhz = index, period_s, [], 0, None
+        self.stop_flag = threading.Event()
+        self.thread = None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
-                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
+            import pynvml
+            pynvml.nvmlInit()
+            uuid = torch.cuda.get_device_properties(self.index).uuid
+            try:
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + str(uuid)).encode())
+            except Exception:  # noqa: BLE001
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.nv = pynvml
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception:  # noqa: BLE001
+            self.nv = None
+            return
+        self.thread = threading.Thread(target=self._loop, daemon=True)
+        self.thread.start()
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+    def _sample(self):
+        self.sm.append(float(self.nv.nvmlDeviceGetClockInfo(self.handle, self.nv.NVML_CLOCK_SM)))
+        self.bits |= int(self.nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
+
+    def _loop(self):
+        while not self.stop_flag.is_set():
+            try:
+                self._sample()
+            except Exception:  # noqa: BLE001
+                return
+            time.sleep(self.period)
 
     def stop(self):
-        if self.proc is None:
+        if getattr(self, "nv", None) is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
-        self.proc.terminate()
+        self.stop_flag.set()
+        self.thread.join(timeout=2)
         try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
-        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in self.rows)]
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(sm)}
+            self._sample()
+        except Exception:  # noqa: BLE001
+            pass
+        reasons = [n for b, n in self.REASONS.items() if self.bits & b]
+        return {"sm_mhz": statistics.median(self.sm) if self.sm else None, "sm_max_mhz": self.max_mhz,
+                "reasons": reasons, "samples": len(self.sm)}
 
 
 def cpu_reference_sample(shape, ids, wts, seed, iters, tokens=128):
@@ -192,8 +206,10 @@ def main():
     ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
 
     def step_resident(i, marks=None):
-        plan = layer.prepare(ids_d, w_d, marks) if marks else layer.prepare(ids_d, w_d)
-        return layer.forward(xs_dev[i % n_x], plan, marks) if marks else layer.forward(xs_dev[i % n_x], plan)
+        if marks is None:
+            return layer.step(ids_d, w_d, xs_dev[i % n_x])
+        plan = layer.prepare(ids_d, w_d, marks)
+        return layer.forward(xs_dev[i % n_x], plan, marks)
 
     ids_in = torch.empty_like(ids_d)
     w_in = torch.empty_like(w_d)
@@ -203,7 +219,7 @@ def main():
         ids_in.copy_(ids_pin, non_blocking=True)
         w_in.copy_(w_pin, non_blocking=True)
         x_in.copy_(xs_host[i % n_x], non_blocking=True)
-        y = layer.forward(x_in, layer.prepare(ids_in, w_in))
+        y = layer.step(ids_in, w_in, x_in)
         y_pin.copy_(y, non_blocking=True)
 
     # ---- device-resident steps (value) + per-kernel brackets (roofline)
@@ -212,23 +228,28 @@ def main():
     layer.check()
     sampler = ClockSampler(local_rank)
     names = ("start", "plan_comm", "place", "plan", "dispatch", "act", "combine")
-    evs = [{n: ev() for n in names} for _ in range(args.steps)]
     launches0 = layer.gpu_launches
     barrier()
     sampler.start()
     t_begin, t_end = ev(), ev()
     t_begin.record()
     for i in range(args.steps):
-        e = evs[i]
-        e["start"].record()
-        step_resident(i, lambda n, e=e: e[n].record())
+        step_resident(i)
     t_end.record()
     barrier()
-    clocks = sampler.stop()
     launches = layer.gpu_launches - launches0
     layer.check()
     ms_total = max_over_ranks(t_begin.elapsed_time(t_end))
     ms_step = ms_total / args.steps
+    # per-kernel brackets (the reference's marks): the same steps again, phase by phase, events between
+    evs = [{n: ev() for n in names} for _ in range(args.steps)]
+    barrier()
+    for i in range(args.steps):
+        e = evs[i]
+        e["start"].record()
+        step_resident(i, lambda n, e=e: e[n].record())
+    barrier()
+    clocks = sampler.stop()
     gemm1_ms = statistics.mean(e["plan"].elapsed_time(e["dispatch"]) for e in evs)
     plan_ms = statistics.mean(e["start"].elapsed_time(e["plan"]) for e in evs)
     comb_ms = statistics.mean(e["act"].elapsed_time(e["combine"]) for e in evs)

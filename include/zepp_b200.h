@@ -71,6 +71,10 @@ int zepp_layer_prepare_phase(zepp_layer* layer, int phase, const int32_t* topk_i
  * Phases: 0 publish x, 1 dispatch GEMM (+pull), 2 combine GEMM (+push), 3 top-k reduce into y. */
 int zepp_layer_forward(zepp_layer* layer, const void* x_dev, void* y_dev, void* stream);
 int zepp_layer_forward_phase(zepp_layer* layer, int phase, const void* x_dev, void* y_dev, void* stream);
+/* prepare + forward in one call (what bench/replay.py:147-149 does per iteration).  topk_ids_dev and
+ * topk_weights_dev are read in place by the step's kernels: keep them unchanged until the step ran. */
+int zepp_layer_step(zepp_layer* layer, const int32_t* topk_ids_dev, const float* topk_weights_dev, const void* x_dev,
+                    void* y_dev, void* stream);
 
 /* Deferred verdict (src/core/verdict.h): synchronises `stream`, copies the 8 status words
  * (error bits, what/peer/epoch of a wait that gave up, violation mask) and clears the error bits. */

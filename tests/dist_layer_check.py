@@ -1,0 +1,68 @@
+"""Run under torch.distributed.run with one process per GPU: builds the layer across real GPUs
+(CUDA IPC arenas, peer loads / stores over NVLink), runs a few steps and checks every rank's
+output against the CPU oracle.  Used by tests/test_multi_gpu.py; prints one line per rank."""
+import argparse
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--strategy", default="overlap")
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--tokens", type=int, default=64)
+    ap.add_argument("--ranks-per-node", type=int, default=0)
+    a = ap.parse_args()
+    from oracle import layer as ol
+    from zepp_b200 import EPMoE, EPMoEConfig, ModelShape
+    from zepp_b200 import workloads as wl
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
+    shape = ModelShape(32, 8, 512, 256, act="swiglu")
+    S = a.tokens
+    cfg = EPMoEConfig(shape=shape, ranks=world, ranks_per_node=a.ranks_per_node or world, max_tokens_per_rank=S,
+                      comm_strategy=a.strategy)
+    gen = torch.Generator().manual_seed(5)
+    p = wl.popularity(shape.num_experts, 1.0, gen)
+    ids, wts = wl.routing(world, S, shape.topk, p, gen)
+    layer = EPMoE(cfg, dist.group.WORLD, ids, ids)
+    W1 = torch.stack([wl.expert_w1(e, shape) for e in range(shape.num_experts)])
+    W2 = torch.stack([wl.expert_w2(e, shape) for e in range(shape.num_experts)])
+    layer.load_weights(lambda e: W1[e], lambda e: W2[e])
+    layer.prime(ids[rank].cuda(), wts[rank].cuda())
+    ok = True
+    worst = 0.0
+    for step in range(a.steps):
+        if step:
+            ids, wts = wl.routing(world, S, shape.topk, p, gen)
+        x = wl.tokens(rank, S, shape.hidden, seed=step)
+        if step % 2 == 0:
+            plan = layer.prepare(ids[rank].cuda(), wts[rank].cuda())
+            y = layer.forward(x.cuda(), plan)
+        else:
+            y = layer.step(ids[rank].cuda(), wts[rank].cuda(), x.cuda())
+        layer.check()
+        ref = ol.moe_reference_fp32(x, ids[rank], wts[rank], W1, W2)
+        err = float((y.float().cpu() - ref).abs().max())
+        worst = max(worst, err)
+        ok &= bool(torch.allclose(y.float().cpu(), ref, rtol=2e-2, atol=2e-2))
+    flag = torch.tensor([0 if ok else 1], device="cuda")
+    dist.all_reduce(flag)
+    print(f"[dist_layer_check] rank {rank}/{world} {a.strategy}: {'PASS' if ok else 'FAIL'} max|err| {worst:.4g}", flush=True)
+    layer.close()
+    dist.barrier()
+    dist.destroy_process_group()
+    sys.exit(0 if int(flag) == 0 else 1)
+
+
+if __name__ == "__main__":
+    main()

@@ -31,6 +31,7 @@ constexpr int kTileK = 64;        // bf16 elements per smem row = 128 bytes = on
 constexpr int kWTileBytes = kTileM * kTileK * 2;   // 16 KB
 constexpr int kXTileBytes = kTileN * kTileK * 2;   // 16 KB
 constexpr int kAccStages = 2;
+constexpr int kMaxTilesSmem = 1024;   // token tiles of one rank and step held in shared memory
 
 enum GemmMode : int { MODE_GATE_UP_SWIGLU = 0, MODE_SINGLE_GELU = 1, MODE_DOWN_COMBINE = 2 };
 
@@ -118,13 +119,26 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
   __shared__ __align__(8) uint64_t acc_empty_bar[kAccStages];
   __shared__ uint32_t tmem_base_smem;
   __shared__ int abort_flag;
+  __shared__ int s_group[kMaxTilesSmem], s_row0[kMaxTilesSmem], s_rows[kMaxTilesSmem];
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const bool violation = a.status != nullptr && a.status[ST_VIOLATION] != 0ull;
-  const int n_tiles = violation ? 0 : *a.tt.n_tiles;     // a step over capacity computes nothing
+  int n_tiles = violation ? 0 : *a.tt.n_tiles;           // a step over capacity computes nothing
+  if (n_tiles > kMaxTilesSmem) n_tiles = kMaxTilesSmem;   // (the host sizes max_tiles below this)
   const int total_items = n_tiles * a.n_feat_tiles;
   const int k_blocks = a.k_extent / kTileK;
+  // balanced persistent schedule: the items are spread over the fewest CTAs that still finish in
+  // ceil(items / grid) rounds, so no round runs with a mostly idle machine
+  const int rounds = (total_items + (int)gridDim.x - 1) / (int)gridDim.x;
+  const int active_ctas = rounds > 0 ? (total_items + rounds - 1) / rounds : 1;
+  const int item_stride = active_ctas;
+  const int item_first = (int)blockIdx.x < active_ctas ? (int)blockIdx.x : total_items;
+  for (int i = threadIdx.x; i < n_tiles; i += blockDim.x) {
+    s_group[i] = a.tt.tile_group[i];
+    s_row0[i] = a.tt.tile_row0[i];
+    s_rows[i] = a.tt.tile_rows[i];
+  }
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -159,12 +173,12 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      for (int item = blockIdx.x; item < total_items && !*abortp; item += gridDim.x) {
+      for (int item = item_first; item < total_items && !*abortp; item += item_stride) {
         const int ti = item / a.n_feat_tiles;
         const int j = item - ti * a.n_feat_tiles;
-        const int grp = a.tt.tile_group[ti];
-        const int row0 = a.tt.tile_row0[ti];
-        const int rows = a.tt.tile_rows[ti];
+        const int grp = s_group[ti];
+        const int row0 = s_row0[ti];
+        const int rows = s_rows[ti];
         const CUtensorMap* tmx = rows <= 32 ? &tm_x32 : (rows <= 64 ? &tm_x64 : &tm_x128);
         const uint32_t x_bytes = (rows <= 32 ? 32u : (rows <= 64 ? 64u : 128u)) * (kTileK * 2);
         const uint32_t tx = (Cfg::kDual ? 2u : 1u) * kWTileBytes + x_bytes;
@@ -207,9 +221,9 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
-      for (int item = blockIdx.x; item < total_items && !*abortp; item += gridDim.x) {
+      for (int item = item_first; item < total_items && !*abortp; item += item_stride) {
         const int ti = item / a.n_feat_tiles;
-        const int rows = a.tt.tile_rows[ti];
+        const int rows = s_rows[ti];
         const uint32_t n_mma = (uint32_t)((rows + 15) & ~15);
         const uint32_t idesc = make_idesc_bf16_m128(n_mma);
         if (!mbar_wait_bounded(&acc_empty_bar[acc], acc_phase ^ 1, abortp, a.mbar_limit)) {
@@ -252,11 +266,11 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     const int quad = warp & 3;                  // TMEM lane quadrant this warp may read
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+    for (int item = item_first; item < total_items; item += item_stride) {
       const int ti = item / a.n_feat_tiles;
       const int j = item - ti * a.n_feat_tiles;
-      const int row0 = a.tt.tile_row0[ti];
-      const int rows = a.tt.tile_rows[ti];
+      const int row0 = s_row0[ti];
+      const int rows = s_rows[ti];
       int got = 0;
       if (lane == 0) got = mbar_wait_bounded(&acc_full_bar[acc], acc_phase, abortp, a.mbar_limit) ? 1 : 0;
       got = __shfl_sync(0xffffffffu, got, 0);
@@ -340,8 +354,8 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         const int my_warp = blockIdx.x * 4 + gw;
         int base = 0;
         for (int ti = 0; ti < n_tiles; ++ti) {
-          const int row0 = a.tt.tile_row0[ti];
-          const int rows = a.tt.tile_rows[ti];
+          const int row0 = s_row0[ti];
+          const int rows = s_rows[ti];
           int first = (my_warp - base) % n_warps;
           if (first < 0) first += n_warps;
           base += rows;

@@ -117,16 +117,17 @@ __global__ void __launch_bounds__(kMetaThreads) meta_pass1_kernel(MetaArgs a) {
   for (int i = threadIdx.x; i < R + NN; i += blockDim.x) tu[i] = ucs[i];
 }
 
-// Exact demands of a step (python/zepp/capacity.py:30-55) by one thread; R <= 64.
-__device__ void demands_serial(const int* sps, const int* uc, int W, int L, int gpe, int relay_slots, int direct,
-                               const long long* caps, long long* out) {
-  const int NN = W / L, E_virt = W * gpe;
+// Exact demands of a step (python/zepp/capacity.py:30-55) from chunks[s][d] (rows from source s to
+// destination d, shared memory) and the unique counts; run by one thread (R <= 64; the single-node
+// case touches only the R x R chunk table).
+__device__ void demands_from_chunks(const int* chunks, const int* uc, int W, int L, int relay_slots, int direct,
+                                    const long long* caps, long long* out) {
+  const int NN = W / L;
   long long recv_rows = 0, pair = 0;
   for (int d = 0; d < W; ++d) {
     long long col = 0;
     for (int s = 0; s < W; ++s) {
-      long long ch = 0;
-      for (int e = 0; e < gpe; ++e) ch += sps[s * E_virt + d * gpe + e];
+      const long long ch = chunks[s * W + d];
       col += ch;
       if (ch > pair) pair = ch;
     }
@@ -152,8 +153,7 @@ __device__ void demands_serial(const int* sps, const int* uc, int W, int L, int 
           const long long chunk = T / L + (k < T % L ? 1 : 0);
           st += chunk;
           if (chunk > relay) relay = chunk;
-          for (int ls = 0; ls < L; ++ls)
-            for (int e = 0; e < gpe; ++e) cv += sps[(ns * L + k) * E_virt + (n * L + ls) * gpe + e];
+          for (int ls = 0; ls < L; ++ls) cv += chunks[(ns * L + k) * W + n * L + ls];
           wr += uc[(ns * L + k) * ucw + W + n];
         }
         if (st > stage) stage = st;
@@ -170,9 +170,8 @@ __device__ void demands_serial(const int* sps, const int* uc, int W, int L, int 
     if (dem[6] > caps[7]) mask |= 0x80;
   } else {
     const int di[7] = {0, 1, 2, 3, 0, 4, 5};
-    const int ci[7] = {0, 1, 2, 3, 4, 5, 6};
     for (int b = 0; b < 7; ++b)
-      if (dem[di[b]] > caps[ci[b]]) mask |= 1ll << b;
+      if (dem[di[b]] > caps[b]) mask |= 1ll << b;
   }
   out[7] = mask;
 }
@@ -182,12 +181,40 @@ __device__ __forceinline__ long long region_rows(const int* uc, int W, int L, in
   return (s / L == d / L) ? uc[s * (W + NN) + d] : uc[s * (W + NN) + W + d / L];
 }
 
+// block-wide exclusive scan of one int per thread (blockDim.x <= 1024); returns the exclusive
+// prefix, *total gets the sum
+__device__ __forceinline__ int block_exclusive_scan(int v, int* warp_tot, int* total) {
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  int incl = v;
+  for (int off = 1; off < 32; off <<= 1) {
+    const int u = __shfl_up_sync(0xffffffffu, incl, off);
+    if (lane >= off) incl += u;
+  }
+  __syncthreads();
+  if (lane == 31) warp_tot[wid] = incl;
+  __syncthreads();
+  if (wid == 0) {
+    const int t = lane < (int)(blockDim.x >> 5) ? warp_tot[lane] : 0;
+    int inc2 = t;
+    for (int off = 1; off < 32; off <<= 1) {
+      const int u = __shfl_up_sync(0xffffffffu, inc2, off);
+      if (lane >= off) inc2 += u;
+    }
+    warp_tot[lane] = inc2 - t;
+    if (lane == 31) warp_tot[32] = inc2;
+  }
+  __syncthreads();
+  *total = warp_tot[32];
+  return warp_tot[wid] + incl - v;
+}
+
 __global__ void __launch_bounds__(kMetaThreads) meta_scan_kernel(MetaArgs a) {
+  extern __shared__ int chunks[];        // [R*R] rows from source s to destination rank d
   const int R = a.R, NN = a.R / a.L, E_virt = a.R * a.gpe, ucw = R + NN;
   const int n_blocks = R * a.tiles_per_src;
-  __shared__ int warp_tot[32];
+  __shared__ int warp_tot[33];
   __shared__ long long viol;
-  // per source splits, totals, tile bases (in place)
+  // per source splits, totals
   for (int e = threadIdx.x; e < E_virt; e += blockDim.x) {
     int tot = 0;
     for (int s = 0; s < R; ++s) {
@@ -205,6 +232,12 @@ __global__ void __launch_bounds__(kMetaThreads) meta_scan_kernel(MetaArgs a) {
     a.uc[i] = acc;
   }
   __syncthreads();
+  for (int i = threadIdx.x; i < R * R; i += blockDim.x) {
+    const int s = i / R, d = i - s * R;
+    int acc = 0;
+    for (int e = 0; e < a.gpe; ++e) acc += a.sps[s * E_virt + d * a.gpe + e];
+    chunks[i] = acc;
+  }
   // exclusive scan of splits -> expert_base (E_virt <= 4 * blockDim)
   {
     const int per = (E_virt + blockDim.x - 1) / blockDim.x;
@@ -212,31 +245,14 @@ __global__ void __launch_bounds__(kMetaThreads) meta_scan_kernel(MetaArgs a) {
     int local = 0;
     for (int q = 0; q < per; ++q)
       if (lo + q < E_virt) local += a.splits[lo + q];
-    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    int incl = local;
-    for (int off = 1; off < 32; off <<= 1) {
-      const int v = __shfl_up_sync(0xffffffffu, incl, off);
-      if (lane >= off) incl += v;
-    }
-    if (lane == 31) warp_tot[wid] = incl;
-    __syncthreads();
-    if (wid == 0) {
-      int v = lane < (int)(blockDim.x >> 5) ? warp_tot[lane] : 0;
-      int inc2 = v;
-      for (int off = 1; off < 32; off <<= 1) {
-        const int u = __shfl_up_sync(0xffffffffu, inc2, off);
-        if (lane >= off) inc2 += u;
-      }
-      warp_tot[lane] = inc2 - v;
-    }
-    __syncthreads();
-    int run = warp_tot[wid] + incl - local;
+    int total;
+    int run = block_exclusive_scan(local, warp_tot, &total);
     for (int q = 0; q < per; ++q)
       if (lo + q < E_virt) { a.expert_base[lo + q] = run; run += a.splits[lo + q]; }
-    if (threadIdx.x == blockDim.x - 1) a.expert_base[E_virt] = run;
+    if (threadIdx.x == 0) a.expert_base[E_virt] = total;
   }
   __syncthreads();
-  for (int e = threadIdx.x; e < E_virt; e += blockDim.x) {
+  for (int e = threadIdx.x; e < E_virt; e += blockDim.x) {      // tile histograms -> tile bases, in place
     int run = a.expert_base[e];
     for (int b = 0; b < n_blocks; ++b) {
       const int h = a.tile_hist[(size_t)b * E_virt + e];
@@ -246,7 +262,7 @@ __global__ void __launch_bounds__(kMetaThreads) meta_scan_kernel(MetaArgs a) {
   }
   if (threadIdx.x == 0) {
     long long out[8];
-    demands_serial(a.sps, a.uc, R, a.L, a.gpe, a.relay_slots, a.direct, a.caps, out);
+    demands_from_chunks(chunks, a.uc, R, a.L, a.relay_slots, a.direct, a.caps, out);
     for (int i = 0; i < 8; ++i) a.demands[i] = out[i];
     viol = out[7];
     if (a.status) {
@@ -255,33 +271,39 @@ __global__ void __launch_bounds__(kMetaThreads) meta_scan_kernel(MetaArgs a) {
     }
   }
   __syncthreads();
-  // ---- this rank's GEMM schedule: token tiles of its groups in row order; groups marked as
-  //      moved-in (bit 30 of their schedule word) are placed last (their weights land late)
-  if (threadIdx.x == 0 && a.n_tiles != nullptr) {
+  // ---- this rank's GEMM schedule: token tiles of its groups in row order, one thread per group;
+  //      groups marked as moved-in (bit 30 of their schedule word) go last (their weights land late)
+  if (a.n_tiles != nullptr) {
     const int g0 = a.my_rank * a.gpe;
     const int m_start = a.expert_base[g0];
     const int m_this = a.expert_base[g0 + a.gpe] - m_start;
-    a.m_this[0] = m_this;
-    a.m_this[1] = m_start;
-    int nt = 0;
-    if (viol == 0 && m_this <= a.recv_cap) {
-      for (int pass = 0; pass < 2; ++pass) {
-        for (int e = 1; e < a.gpe; ++e) {
-          const bool late = a.group_order != nullptr && ((a.group_order[e] >> 30) & 1);
-          if ((pass == 1) != late) continue;
-          const int me = a.splits[g0 + e];
-          const int off = a.expert_base[g0 + e] - m_start;
-          for (int r = 0; r < me && nt < a.max_tiles; r += kTileRowsMax) {
-            a.tile_group[nt] = e;
-            a.tile_row0[nt] = off + r;
-            a.tile_rows[nt] = min(kTileRowsMax, me - r);
-            a.tile_ready[nt] = 0u;
-            ++nt;
-          }
-        }
+    const bool run_ok = viol == 0 && m_this <= a.recv_cap;
+    const int e = threadIdx.x;                   // gpe <= blockDim.x
+    int me = 0, late = 0;
+    if (e >= 1 && e < a.gpe && run_ok) {
+      me = a.splits[g0 + e];
+      late = a.group_order != nullptr ? ((a.group_order[e] >> 30) & 1) : 0;
+    }
+    const int nt = (me + kTileRowsMax - 1) / kTileRowsMax;
+    int tot_early, tot_late;
+    const int pre_early = block_exclusive_scan(late ? 0 : nt, warp_tot, &tot_early);
+    const int pre_late = block_exclusive_scan(late ? nt : 0, warp_tot, &tot_late);
+    const int first = late ? tot_early + pre_late : pre_early;
+    const int off = e < a.gpe ? a.expert_base[g0 + (e < a.gpe ? e : 0)] - m_start : 0;
+    for (int t = 0; t < nt; ++t) {
+      const int slot = first + t;
+      if (slot < a.max_tiles) {
+        a.tile_group[slot] = e;
+        a.tile_row0[slot] = off + t * kTileRowsMax;
+        a.tile_rows[slot] = min(kTileRowsMax, me - t * kTileRowsMax);
+        a.tile_ready[slot] = 0u;
       }
     }
-    *a.n_tiles = nt;
+    if (threadIdx.x == 0) {
+      a.m_this[0] = m_this;
+      a.m_this[1] = m_start;
+      *a.n_tiles = min(tot_early + tot_late, a.max_tiles);
+    }
   }
   // ---- plan heads
   if (threadIdx.x == 32 && a.dplan != nullptr) {
@@ -297,8 +319,7 @@ __global__ void __launch_bounds__(kMetaThreads) meta_scan_kernel(MetaArgs a) {
     }
     for (int s = 0; s < W; ++s) {
       for (int d = 0; d < W; ++d) {
-        long long cv = 0;
-        for (int e = 0; e < a.gpe; ++e) cv += a.sps[s * E_virt + d * a.gpe + e];
+        const long long cv = chunks[s * W + d];
         const long long uv = a.uc[s * ucw + d];
         if (!(uv >= 0 && uv <= cv && ((uv > 0) == (cv > 0)))) err |= 4;
         if (uv > a.uc[s * ucw + W + d / L]) err |= 8;
@@ -312,8 +333,7 @@ __global__ void __launch_bounds__(kMetaThreads) meta_scan_kernel(MetaArgs a) {
     long long* P = a.dplan;
     long long seg = 0;
     int si = 0;
-    P[8 + 0] = 0;
-    long long seg_me = 0, seg_tab[128];
+    long long seg_tab[130];
     seg_tab[0] = 0;
     for (int n = 0; n < NN; ++n) {
       if (n == me_n) {
@@ -336,13 +356,11 @@ __global__ void __launch_bounds__(kMetaThreads) meta_scan_kernel(MetaArgs a) {
     if (max_col > a.caps[1]) err |= 16;
     if (seg_tab[nseg] > a.copies_per_rank) err |= 32;
     long long m0 = 0;
-    for (int s = 0; s < W; ++s)
-      for (int e = 0; e < a.gpe; ++e) m0 += a.sps[s * E_virt + rank * a.gpe + e];
+    for (int s = 0; s < W; ++s) m0 += chunks[s * W + rank];
     long long off_me = 0;
     for (int s = 0; s < rank; ++s) off_me += region_rows(a.uc, W, L, s, rank);
-    seg_me = seg_tab[me_n + me_l];
-    P[0] = m0; P[1] = seg_tab[nseg]; P[2] = a.uc[rank * ucw + rank]; P[3] = seg_me; P[4] = off_me; P[5] = err;
-    P[6] = 0; P[7] = 0;
+    P[0] = m0; P[1] = seg_tab[nseg]; P[2] = a.uc[rank * ucw + rank]; P[3] = seg_tab[me_n + me_l]; P[4] = off_me;
+    P[5] = err; P[6] = 0; P[7] = 0;
   }
   if (threadIdx.x == 64 && a.cplan != nullptr) {
     // combine tables on one node (python/zepp/routing.py:656-669): C[s][d] rows owner s returns to home d
@@ -354,22 +372,18 @@ __global__ void __launch_bounds__(kMetaThreads) meta_scan_kernel(MetaArgs a) {
     long long acc = 0;
     so[0] = 0;
     for (int d = 0; d < W; ++d) {
-      long long c = 0;
-      for (int e = 0; e < a.gpe; ++e) c += a.sps[d * E_virt + rank * a.gpe + e];
+      const long long c = chunks[d * W + rank];
       sr[d] = c;
       acc += c;
       so[d + 1] = acc;
       long long before = 0;
-      for (int s = 0; s < rank; ++s)
-        for (int e = 0; e < a.gpe; ++e) before += a.sps[d * E_virt + s * a.gpe + e];
+      for (int s = 0; s < rank; ++s) before += chunks[d * W + s];
       dof[d] = before;
     }
     acc = 0;
     lo[0] = 0;
     for (int s = 0; s < W; ++s) {
-      long long c = 0;
-      for (int e = 0; e < a.gpe; ++e) c += a.sps[rank * E_virt + s * a.gpe + e];
-      acc += c;
+      acc += chunks[rank * W + s];
       lo[s + 1] = acc;
     }
   }
@@ -378,32 +392,36 @@ __global__ void __launch_bounds__(kMetaThreads) meta_scan_kernel(MetaArgs a) {
 __global__ void __launch_bounds__(kMetaThreads) meta_pass2_kernel(MetaArgs a) {
   extern __shared__ int sm[];
   const int E_virt = a.R * a.gpe, SK = a.S * a.K;
-  int* cnt = sm;                          // running position per expert inside this tile
   const int src = blockIdx.x / a.tiles_per_src;
   const int tb = blockIdx.x - src * a.tiles_per_src;
   const int* tbase = a.tile_hist + (size_t)blockIdx.x * E_virt;
-  for (int e = threadIdx.x; e < E_virt; e += blockDim.x) cnt[e] = tbase[e];
-  __syncthreads();
   const int T = a.tokens_per_tile * a.K;
+  const int n_warps = (T + 31) / 32;
+  int* wc = sm;                           // [n_warps][E_virt] copies of expert e in warp w, then their base
+  for (int i = threadIdx.x; i < n_warps * E_virt; i += blockDim.x) wc[i] = 0;
+  __syncthreads();
   const int n = tb * T + threadIdx.x;
   const bool valid = threadIdx.x < T && n < SK;
   const size_t flat = (size_t)src * SK + (valid ? n : 0);
   const int e = valid ? a.vce[flat] : -1 - (int)(threadIdx.x & 31);     // invalid lanes never match
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-  const int n_warps = (T + 31) / 32;
-  int idx = -1;
-  for (int w = 0; w < n_warps; ++w) {
-    if (wid == w) {
-      const unsigned m = __match_any_sync(0xffffffffu, e);
-      const int leader = __ffs(m) - 1;
-      int off = 0;
-      if (valid && lane == leader) { off = cnt[e]; cnt[e] = off + __popc(m); }
-      off = __shfl_sync(0xffffffffu, off, leader);
-      idx = off + __popc(m & ((1u << lane) - 1u));
-    }
-    __syncthreads();
+  unsigned m = 0;
+  if (wid < n_warps) {
+    m = __match_any_sync(0xffffffffu, e);
+    if (valid && lane == __ffs(m) - 1) wc[wid * E_virt + e] = __popc(m);
   }
+  __syncthreads();
+  for (int x = threadIdx.x; x < E_virt; x += blockDim.x) {      // exclusive prefix over the tile's warps
+    int run = tbase[x];
+    for (int w = 0; w < n_warps; ++w) {
+      const int c = wc[w * E_virt + x];
+      wc[w * E_virt + x] = run;
+      run += c;
+    }
+  }
+  __syncthreads();
   if (!valid) return;
+  const int idx = wc[wid * E_virt + e] + __popc(m & ((1u << lane) - 1u));
   a.scatter_index[flat] = idx;
   if (a.row_tok != nullptr && e / a.gpe == a.my_rank) {
     const int r = idx - a.m_this[1];

@@ -47,8 +47,9 @@ struct PeerTable {
 // ---------------------------------------------------------------------------------------
 __global__ void loads_publish_kernel(const int* __restrict__ topk_own, int n_entries, int G, int rank, int world,
                                      PeerTable dst, PeerTable flags, unsigned long long epoch,
-                                     unsigned long long* status) {
+                                     unsigned long long* status, long long* route_stats) {
   extern __shared__ int hist[];
+  if (route_stats != nullptr && threadIdx.x < 4) route_stats[threadIdx.x] = 0;
   for (int g = threadIdx.x; g < G; g += blockDim.x) hist[g] = 0;
   __syncthreads();
   for (int n = threadIdx.x; n < n_entries; n += blockDim.x) {
@@ -118,8 +119,22 @@ __global__ void __launch_bounds__(256) route_kernel(RouteArgs a) {
   const int wib = threadIdx.x >> 5;
   const int g = blockIdx.x * warps_per_block + wib;
   const int lane = threadIdx.x & 31;
-  if (g >= a.G) return;
   const int R = a.R, L = a.L, NN = R / L, G = a.G;
+  // ---- entries of single-replica experts need no ordinal: every thread of the grid fills a
+  //      slice of them straight from the placement (the only replica is the first valid l2p entry)
+  if (a.topk_own != nullptr)
+  for (int n = blockIdx.x * blockDim.x + threadIdx.x; n < a.n_entries; n += gridDim.x * blockDim.x) {
+    const int e = a.topk_own[n];
+    if (e < 0 || e >= G) continue;
+    const int cnt = min(a.lcnts[e], R);
+    int found = 0, p0 = -1;
+    for (int j = 0; j < cnt; ++j) {
+      const int p = a.l2p[e * R + j];
+      if (p >= 0) { if (found == 0) p0 = p; ++found; }
+    }
+    if (found == 1) a.phys_own[n] = p0;
+  }
+  if (g >= a.G) return;
   const int CM = route_cm(R);
   const RouteWs w = route_ws_layout(G, R);
   int* rep = a.ws + w.rep + g * CM;
@@ -237,8 +252,9 @@ __global__ void __launch_bounds__(256) route_kernel(RouteArgs a) {
     extp[lane] = (int)ext;
   }
 
-  // ---- visit order of this source and cumulative takes
   if (a.topk_own == nullptr) return;
+  if (c <= 1) return;
+  // ---- visit order of this source and cumulative takes
   {
     int pr = 1 << 30;
     if (lane < c) {

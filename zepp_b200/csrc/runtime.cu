@@ -225,6 +225,9 @@ struct zepp_layer {
   // tensor maps
   CUtensorMap tm_w1, tm_w2, tm_recv[3], tm_act[3];
   const void* x_self = nullptr;
+  const int* ids_in = nullptr;
+  const float* wts_in = nullptr;
+  bool pass2_attr = false;
 };
 
 static size_t al(size_t v) { return (v + 1023) / 1024 * 1024; }
@@ -342,6 +345,7 @@ extern "C" int zepp_layer_create(zepp_rt* rt, const zepp_layer_cfg* c, zepp_laye
   l->tokens_per_tile = kMetaThreads / l->K;
   l->tiles_per_src = (l->S + l->tokens_per_tile - 1) / l->tokens_per_tile;
   if (l->E_virt > 4 * kMetaThreads) { delete l; return fail("too many virtual experts (%d)", l->E_virt); }
+  if (l->max_tiles > kMaxTilesSmem) { delete l; return fail("recv_cap %d needs more than %d token tiles", l->cap, kMaxTilesSmem); }
   if (layer_alloc(l)) { delete l; return 1; }
   // peer tables
   const int R = l->W;
@@ -437,6 +441,18 @@ static MetaArgs layer_meta_args(zepp_layer* l) {
 }
 
 static size_t meta_smem(int R, int NN, int E_virt) { return (size_t)(E_virt + R + NN) * sizeof(int); }
+static size_t pass2_smem(int tokens_per_tile, int K, int E_virt) {
+  return (size_t)((tokens_per_tile * K + 31) / 32) * E_virt * sizeof(int);
+}
+static int pass2_prepare(size_t bytes) {
+  static size_t granted = 48 * 1024;
+  if (bytes > 200 * 1024) return fail("metadata: %zu bytes of shared memory per tile exceed the SM", bytes);
+  if (bytes > granted) {
+    CU_OK(cudaFuncSetAttribute(meta_pass2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    granted = bytes;
+  }
+  return 0;
+}
 
 extern "C" int zepp_layer_prepare_phase(zepp_layer* l, int phase, const int32_t* ids, const float* wts, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
@@ -446,22 +462,23 @@ extern "C" int zepp_layer_prepare_phase(zepp_layer* l, int phase, const int32_t*
   if (phase == 0) {
     l->epoch += 1;
     const int b = (int)(l->epoch & 1);
-    CU_OK(cudaMemcpyAsync(l->topk_own, ids, (size_t)l->SK * 4, cudaMemcpyDeviceToDevice, st));
-    CU_OK(cudaMemcpyAsync(l->probs_own, wts, (size_t)l->SK * 4, cudaMemcpyDeviceToDevice, st));
-    loads_publish_kernel<<<1, 1024, l->G * sizeof(int), st>>>(l->topk_own, l->SK, l->G, me, R, l->loads_dst[b],
-                                                             l->loads_flag_dst, l->epoch, l->status);
+    // the routing inputs are read in place by this step's kernels (stream order keeps them valid)
+    l->ids_in = ids;
+    l->wts_in = wts;
+    loads_publish_kernel<<<1, 1024, l->G * sizeof(int), st>>>(ids, l->SK, l->G, me, R, l->loads_dst[b],
+                                                             l->loads_flag_dst, l->epoch, l->status, l->route_stats);
     LAUNCH_OK();
     return 0;
   }
   const int b = (int)(l->epoch & 1);
   if (phase == 1) {
     RouteArgs ra{};
-    ra.topk_own = l->topk_own; ra.n_entries = l->SK; ra.loads = l->loads_all[b]; ra.l2p = l->l2p; ra.lcnts = l->lcnts;
+    if (ids) { l->ids_in = ids; l->wts_in = wts; }
+    ra.topk_own = l->ids_in; ra.n_entries = l->SK; ra.loads = l->loads_all[b]; ra.l2p = l->l2p; ra.lcnts = l->lcnts;
     ra.G = l->G; ra.R = R; ra.L = l->L; ra.nlp = l->nlp; ra.my_rank = me;
     ra.c_num = l->cfg.c_num; ra.c_den = l->cfg.c_den; ra.ws = l->route_ws; ra.phys_own = l->phys_own;
     ra.loads_flags = R > 1 ? l->loads_flags : nullptr;
     ra.epoch = l->epoch; ra.limit_ns = l->rt->wait_ns; ra.status = l->status; ra.stats = l->route_stats;
-    CU_OK(cudaMemsetAsync(l->route_stats, 0, 32, st));
     route_kernel<<<(l->G + 7) / 8, 256, 0, st>>>(ra);
     LAUNCH_OK();
     if (l->cfg.swap) {
@@ -481,7 +498,7 @@ extern "C" int zepp_layer_prepare_phase(zepp_layer* l, int phase, const int32_t*
       l->launches++;
     }
     FinishArgs fa{};
-    fa.topk_own = l->topk_own; fa.phys_own = l->phys_own; fa.probs_own = l->probs_own;
+    fa.topk_own = l->ids_in; fa.phys_own = l->phys_own; fa.probs_own = l->wts_in;
     fa.S = l->S; fa.K = l->K; fa.G = l->G; fa.R = R; fa.L = l->L; fa.nlp = l->nlp; fa.my_rank = me;
     fa.ws = l->route_ws; fa.send_row = l->send_row; fa.dst = l->xchg_dst[b]; fa.flags = l->routing_flag_dst;
     fa.world = R; fa.epoch = l->epoch; fa.block_counter = l->counters + 0; fa.status = l->status;
@@ -498,11 +515,13 @@ extern "C" int zepp_layer_prepare_phase(zepp_layer* l, int phase, const int32_t*
     MetaArgs m = layer_meta_args(l);
     const int grid = R * l->tiles_per_src;
     const size_t sm = meta_smem(R, l->NN, l->E_virt);
+    const size_t sm2 = pass2_smem(l->tokens_per_tile, l->K, l->E_virt);
+    if (pass2_prepare(sm2)) return 1;
     meta_pass1_kernel<<<grid, kMetaThreads, sm, st>>>(m);
     LAUNCH_OK();
-    meta_scan_kernel<<<1, kMetaThreads, 0, st>>>(m);
+    meta_scan_kernel<<<1, kMetaThreads, (size_t)R * R * sizeof(int), st>>>(m);
     LAUNCH_OK();
-    meta_pass2_kernel<<<grid, kMetaThreads, sm, st>>>(m);
+    meta_pass2_kernel<<<grid, kMetaThreads, sm2, st>>>(m);
     LAUNCH_OK();
     return 0;
   }
@@ -619,6 +638,11 @@ extern "C" int zepp_layer_forward(zepp_layer* l, const void* x, void* y, void* s
   for (int ph = 0; ph < 4; ++ph)
     if (zepp_layer_forward_phase(l, ph, x, y, stream)) return 1;
   return 0;
+}
+
+extern "C" int zepp_layer_step(zepp_layer* l, const int32_t* ids, const float* wts, const void* x, void* y, void* stream) {
+  if (zepp_layer_prepare(l, ids, wts, stream)) return 1;
+  return zepp_layer_forward(l, x, y, stream);
 }
 
 extern "C" int zepp_layer_status(zepp_layer* l, void* stream, uint64_t out[8]) {
@@ -756,11 +780,14 @@ extern "C" int zepp_routed_meta(const int32_t* gathered, const int32_t* vce_in, 
   m.n_tiles = nullptr; m.row_tok = nullptr; m.status = nullptr; m.routing_flags = nullptr;
   const int grid = (int)tiles;
   const size_t sm = meta_smem(R, NN, E_virt);
+  const size_t sm2 = pass2_smem(m.tokens_per_tile, K, E_virt);
+  if (gpe > kMetaThreads) return fail("routed_meta: too many groups per rank");
+  if (pass2_prepare(sm2)) return 1;
   meta_pass1_kernel<<<grid, kMetaThreads, sm, st>>>(m);
   CU_OK(cudaGetLastError());
-  meta_scan_kernel<<<1, kMetaThreads, 0, st>>>(m);
+  meta_scan_kernel<<<1, kMetaThreads, (size_t)R * R * sizeof(int), st>>>(m);
   CU_OK(cudaGetLastError());
-  meta_pass2_kernel<<<grid, kMetaThreads, sm, st>>>(m);
+  meta_pass2_kernel<<<grid, kMetaThreads, sm2, st>>>(m);
   CU_OK(cudaGetLastError());
   return 0;
 }

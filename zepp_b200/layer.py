@@ -148,11 +148,15 @@ class EPMoE(torch.nn.Module):
         assert ids.shape == (self.cfg.max_tokens_per_rank, self.cfg.shape.topk), tuple(ids.shape)
         return ids, wts
 
-    def prepare(self, topk_ids, topk_weights, marks=Marks(), phase=None):
+    def prepare(self, topk_ids, topk_weights, marks=None, phase=None):
         """Loads exchange -> (swap decision) -> route -> routing exchange -> metadata; returns the Plan.
-        `phase` (0, 1, 2) runs one stage only: ranks emulated inside one process advance in lock step."""
+        `phase` (0, 1, 2) runs one stage only: ranks emulated inside one process advance in lock step.
+        The id / weight tensors are read in place by the step's kernels (keep them unchanged until then)."""
         ids, wts = self._ids(topk_ids, topk_weights)
-        if phase is None:
+        self._keep = (ids, wts)
+        if phase is None and marks is None:
+            self._h.prepare(ids, wts)
+        elif phase is None:
             self._h.prepare(ids, wts, 0)
             marks("plan_comm")
             self._h.prepare(ids, wts, 1)
@@ -169,11 +173,14 @@ class EPMoE(torch.nn.Module):
             self._plan_views = (self._h.table("vce").view(-1, K), self._h.table("probs_all").view(-1, K))
         return Plan(self._plan_views[0], self._plan_views[1], stable=True, epoch=self._epoch)
 
-    def forward(self, x, plan=None, marks=Marks(), phase=None):
+    def forward(self, x, plan=None, marks=None, phase=None):
         assert x.shape == (self.cfg.max_tokens_per_rank, self.cfg.shape.hidden), tuple(x.shape)
         x = x.contiguous()
         if phase is not None:
             self._h.forward(x, self._y, phase)
+            return self._y
+        if marks is None:
+            self._h.forward(x, self._y)
             return self._y
         self._h.forward(x, self._y, 0)
         self._h.forward(x, self._y, 1)
@@ -182,6 +189,14 @@ class EPMoE(torch.nn.Module):
         self._h.forward(x, self._y, 2)
         self._h.forward(x, self._y, 3)
         marks("combine")
+        return self._y
+
+    def step(self, topk_ids, topk_weights, x):
+        """prepare + forward in one runtime call (lowest host overhead)."""
+        ids, wts = self._ids(topk_ids, topk_weights)
+        self._keep = (ids, wts)
+        self._h.step(ids, wts, x.contiguous(), self._y)
+        self._epoch += 1
         return self._y
 
     # -- verdict ----------------------------------------------------------------------------

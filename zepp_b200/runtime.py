@@ -127,6 +127,10 @@ class LayerHandle:
         else:
             check(lib().zepp_layer_forward_phase(a[0], int(phase), *a[1:]))
 
+    def step(self, ids, wts, x, y):
+        check(lib().zepp_layer_step(self.h, ctypes.c_void_p(ids.data_ptr()), ctypes.c_void_p(wts.data_ptr()),
+                                    ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(y.data_ptr()), self._stream()))
+
     def status(self):
         out = (ctypes.c_uint64 * 8)()
         check(lib().zepp_layer_status(self.h, self._stream(), out))
