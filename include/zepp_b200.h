@@ -113,6 +113,18 @@ int zepp_routed_meta(const int32_t* gathered_dev, const int32_t* vce_in_dev, int
                      int32_t* vce_dev, float* probs_all_dev, int32_t* splits_dev, int32_t* scatter_index_dev,
                      int32_t* sps_dev, int32_t* uc_dev, int64_t* demands_dev, int64_t* dplan_dev, int64_t* cplan_dev,
                      void* ws_dev, void* stream);
+/* No counterpart in the reference.  zepp_routed_meta for callers that cannot allocate device memory where they
+ * plan (a server whose own pool holds the whole GPU, a thread that must not block in the allocator): same
+ * arguments minus the workspace; the scratch is a 1 MiB array inside the library image on every GPU that loads
+ * it.  Routings whose scratch need (zepp_meta_workspace_bytes) exceeds 1 MiB are refused with an error.  Calls no
+ * cudaMalloc / cudaFree.  The first call on a device looks up the array's address (make that call before any
+ * stream capture, with the device current).  All calls on a device share the one array: two calls whose
+ * kernels may overlap on the GPU (different streams) race; calls on one stream are safe. */
+int zepp_routed_meta_noalloc(const int32_t* gathered_dev, const int32_t* vce_in_dev, int R, int L, int S, int K,
+                             int nlp, int gpe, int my_rank, int direct, int relay_slots, const int64_t caps[8],
+                             int copies_per_rank, int32_t* vce_dev, float* probs_all_dev, int32_t* splits_dev,
+                             int32_t* scatter_index_dev, int32_t* sps_dev, int32_t* uc_dev, int64_t* demands_dev,
+                             int64_t* dplan_dev, int64_t* cplan_dev, void* stream);
 int zepp_dispatch_plan_words(int L, int NN);
 /* swap_decide (src/planner/swap_decide.cu:81-346): rewrites p2l / l2p in place, fills the result block
  * int64[zepp_swap_decide_out_ints]. */

@@ -6,6 +6,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 #include <new>
 #include <string>
 #include <vector>
@@ -834,4 +835,56 @@ extern "C" int zepp_wait_geq(const uint64_t* flag, uint64_t value, int limit_ms,
                                                       (unsigned long long)limit_ms * 1000000ull, result);
   CU_OK(cudaGetLastError());
   return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// routed metadata without a caller-provided (or any) allocation
+// ---------------------------------------------------------------------------------------------
+// Some hosts of this library cannot allocate device memory at the point where they plan a step: a
+// serving process that handed the whole GPU to its own memory pool at start-up (a cudaMalloc there
+// fails, or stalls every stream behind its implicit device-wide synchronisation), or a planner
+// thread that must never block on the allocator.  zepp_routed_meta needs a scratch workspace from
+// its caller; this variant keeps the scratch in the library image instead: a fixed array in device
+// global memory that every GPU loading the library holds until the process exits.
+constexpr size_t kMetaScratchMaxBytes = 1u << 20;     // 1 MiB per GPU, the stated maximum
+static __device__ __align__(256) unsigned char g_meta_scratch[kMetaScratchMaxBytes];
+
+// In host code `g_meta_scratch` is only a handle of the symbol, never a device address: the
+// address each GPU gave the array is asked for once per device (with that device current).
+static void* g_meta_scratch_addr[kMaxRanks] = {};
+static std::mutex g_meta_scratch_mutex;
+
+extern "C" int zepp_routed_meta_noalloc(const int32_t* gathered, const int32_t* vce_in, int R, int L, int S, int K,
+                                        int nlp, int gpe, int my_rank, int direct, int relay_slots,
+                                        const int64_t caps[8], int copies_per_rank, int32_t* vce, float* probs_all,
+                                        int32_t* splits, int32_t* scatter_index, int32_t* sps, int32_t* uc,
+                                        int64_t* demands, int64_t* dplan, int64_t* cplan, void* stream) {
+  if (R < 1 || R > kMaxRanks || L < 1 || R % L || S < 1 || K < 1 || K > 64 || gpe < 2)
+    return fail("routed_meta_noalloc: bad shape R=%d L=%d S=%d K=%d gpe=%d", R, L, S, K, gpe);
+  const size_t need = zepp_meta_workspace_bytes(R, S, K, gpe);
+  if (need > kMetaScratchMaxBytes)
+    return fail("routed_meta_noalloc: this routing needs %zu bytes of scratch, the built-in scratch holds %zu "
+                "(R=%d S=%d K=%d gpe=%d); use zepp_routed_meta with a caller workspace",
+                need, (size_t)kMetaScratchMaxBytes, R, S, K, gpe);
+  int dev = -1;
+  CU_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxRanks) return fail("routed_meta_noalloc: device ordinal %d out of range", dev);
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_meta_scratch_mutex);
+    if (g_meta_scratch_addr[dev] == nullptr) {
+      // first call on this device: resolve the array's device address (not an allocation)
+      void* p = nullptr;
+      cudaError_t e = cudaGetSymbolAddress(&p, g_meta_scratch);
+      if (e != cudaSuccess || p == nullptr)
+        return fail("routed_meta_noalloc: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
+      g_meta_scratch_addr[dev] = p;
+    }
+    scratch = g_meta_scratch_addr[dev];
+  }
+  // Nothing in the scratch has to start at zero: every word a kernel of this call reads (tile
+  // histograms, tile unique counts, expert bases) is written earlier in the same call, so the
+  // previous call's leftovers are harmless.
+  return zepp_routed_meta(gathered, vce_in, R, L, S, K, nlp, gpe, my_rank, direct, relay_slots, caps, copies_per_rank,
+                          vce, probs_all, splits, scatter_index, sps, uc, demands, dplan, cplan, scratch, stream);
 }
