@@ -61,10 +61,11 @@ struct GemmArgs {
   unsigned long long* const* done_flags;   // [W] peer-mapped flag arrays, or nullptr
   unsigned int* cta_counter;               // self-resetting arrival counter
   int world, rank;
-  unsigned long long epoch;
+  const unsigned long long* epoch_ptr;     // device step counter (the step's epoch; parity picks x buffers)
   // fused gather (dispatch GEMM, overlap strategy)
   const int* row_tok;                      // [cap] global token id (source * S + token) of row r
-  const __nv_bfloat16* const* x_ptrs;      // [W] peer-mapped x buffers [S, H]
+  const __nv_bfloat16* const* x_ptrs;      // [W] peer-mapped x buffers [S, H] of even epochs
+  const __nv_bfloat16* const* x_ptrs_odd;  // ... of odd epochs
   const __nv_bfloat16* x_self;             // this rank's own x (read in place), or nullptr
   const unsigned long long* x_flags;       // [W] local flags: x of source s published for `epoch`
   __nv_bfloat16* recv;                     // [cap, H] local receive buffer (TMA source)
@@ -119,10 +120,13 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
   __shared__ __align__(8) uint64_t acc_empty_bar[kAccStages];
   __shared__ uint32_t tmem_base_smem;
   __shared__ int abort_flag;
-  __shared__ int s_group[kMaxTilesSmem], s_row0[kMaxTilesSmem], s_rows[kMaxTilesSmem];
+  __shared__ int s_row0[kMaxTilesSmem], s_gr[kMaxTilesSmem];      // first row; (group << 9) | rows
+  __shared__ __align__(16) __nv_bfloat16 s_stage[2][32][kTileM];   // epilogue transpose buffers
+  __shared__ int s_epi_ok;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const unsigned long long epoch = a.epoch_ptr != nullptr ? *a.epoch_ptr : 0ull;
   const bool violation = a.status != nullptr && a.status[ST_VIOLATION] != 0ull;
   int n_tiles = violation ? 0 : *a.tt.n_tiles;           // a step over capacity computes nothing
   if (n_tiles > kMaxTilesSmem) n_tiles = kMaxTilesSmem;   // (the host sizes max_tiles below this)
@@ -135,9 +139,8 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
   const int item_stride = active_ctas;
   const int item_first = (int)blockIdx.x < active_ctas ? (int)blockIdx.x : total_items;
   for (int i = threadIdx.x; i < n_tiles; i += blockDim.x) {
-    s_group[i] = a.tt.tile_group[i];
     s_row0[i] = a.tt.tile_row0[i];
-    s_rows[i] = a.tt.tile_rows[i];
+    s_gr[i] = (a.tt.tile_group[i] << 9) | (a.tt.tile_rows[i] & 0x1FF);
   }
 
   if (threadIdx.x == 0) {
@@ -176,9 +179,9 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
       for (int item = item_first; item < total_items && !*abortp; item += item_stride) {
         const int ti = item / a.n_feat_tiles;
         const int j = item - ti * a.n_feat_tiles;
-        const int grp = s_group[ti];
+        const int grp = s_gr[ti] >> 9;
         const int row0 = s_row0[ti];
-        const int rows = s_rows[ti];
+        const int rows = s_gr[ti] & 0x1FF;
         const CUtensorMap* tmx = rows <= 32 ? &tm_x32 : (rows <= 64 ? &tm_x64 : &tm_x128);
         const uint32_t x_bytes = (rows <= 32 ? 32u : (rows <= 64 ? 64u : 128u)) * (kTileK * 2);
         const uint32_t tx = (Cfg::kDual ? 2u : 1u) * kWTileBytes + x_bytes;
@@ -192,7 +195,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             __nanosleep(64);
           }
           if (!ok) {
-            record_timeout(a.status, WAIT_TILE_READY, ti, (long long)a.epoch);
+            record_timeout(a.status, WAIT_TILE_READY, ti, (long long)epoch);
             abort_flag = 1;
             break;
           }
@@ -223,7 +226,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
       uint32_t acc_phase = 0;
       for (int item = item_first; item < total_items && !*abortp; item += item_stride) {
         const int ti = item / a.n_feat_tiles;
-        const int rows = s_rows[ti];
+        const int rows = s_gr[ti] & 0x1FF;
         const uint32_t n_mma = (uint32_t)((rows + 15) & ~15);
         const uint32_t idesc = make_idesc_bf16_m128(n_mma);
         if (!mbar_wait_bounded(&acc_empty_bar[acc], acc_phase ^ 1, abortp, a.mbar_limit)) {
@@ -263,68 +266,83 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     __syncwarp();
   } else if (warp < 6) {
     // ------------------------------------------------------------------ epilogue (4 warps)
+    // TMEM holds D[feature, token]; a thread owns one feature (lane of its quadrant) and reads 32
+    // tokens at a time.  The 32 x 128 chunk is transposed through shared memory so that global
+    // stores are 16-byte vectors covering 256 contiguous bytes of a token row (full lines for the
+    // local activation buffer and for the home rank's panel across NVLink).
     const int quad = warp & 3;                  // TMEM lane quadrant this warp may read
+    const int ew = warp - 2;                    // 0..3 among the epilogue warps
     int acc = 0;
     uint32_t acc_phase = 0;
+    int buf = 0;
     for (int item = item_first; item < total_items; item += item_stride) {
       const int ti = item / a.n_feat_tiles;
       const int j = item - ti * a.n_feat_tiles;
       const int row0 = s_row0[ti];
-      const int rows = s_rows[ti];
-      int got = 0;
-      if (lane == 0) got = mbar_wait_bounded(&acc_full_bar[acc], acc_phase, abortp, a.mbar_limit) ? 1 : 0;
-      got = __shfl_sync(0xffffffffu, got, 0);
-      if (!got) {
-        if (lane == 0 && !*abortp) {
-          record_timeout(a.status, WAIT_TMEM_FULL, item, acc);
-          abort_flag = 1;
+      const int rows = s_gr[ti] & 0x1FF;
+      // one warp waits for the accumulator and tells the others, so all four take the same branch
+      if (ew == 0) {
+        int got = 0;
+        if (lane == 0) {
+          got = mbar_wait_bounded(&acc_full_bar[acc], acc_phase, abortp, a.mbar_limit) ? 1 : 0;
+          if (!got && !*abortp) {
+            record_timeout(a.status, WAIT_TMEM_FULL, item, acc);
+            abort_flag = 1;
+          }
+          s_epi_ok = got;
         }
-        break;
       }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (!s_epi_ok) break;
       tc_fence_after();
       const uint32_t t0 = tmem_base + acc * Cfg::kAccCols + ((uint32_t)(quad * 32) << 16);
-      const int feat = j * kTileM + quad * 32 + lane;       // output feature of this thread
+      const int fcol = quad * 32 + lane;        // feature inside the 128-feature tile
       for (int c0 = 0; c0 < rows; c0 += 32) {
         uint32_t g[32];
+        __nv_bfloat16 (*stg)[kTileM] = s_stage[buf];
         tmem_ld_32x32(t0 + c0, g);
         if (MODE == MODE_GATE_UP_SWIGLU) {
           uint32_t u[32];
           tmem_ld_32x32(t0 + kTileN + c0, u);
           tmem_ld_wait();
-          __nv_bfloat16* out = a.act + (size_t)(row0 + c0) * a.ld_act + feat;
 #pragma unroll
-          for (int n = 0; n < 32; ++n)
-            if (c0 + n < rows) out[(size_t)n * a.ld_act] = swiglu_bf16(__uint_as_float(g[n]), __uint_as_float(u[n]));
+          for (int n = 0; n < 32; ++n) stg[n][fcol] = swiglu_bf16(__uint_as_float(g[n]), __uint_as_float(u[n]));
         } else if (MODE == MODE_SINGLE_GELU) {
           tmem_ld_wait();
-          __nv_bfloat16* out = a.act + (size_t)(row0 + c0) * a.ld_act + feat;
 #pragma unroll
-          for (int n = 0; n < 32; ++n)
-            if (c0 + n < rows) out[(size_t)n * a.ld_act] = gelu_bf16(__uint_as_float(g[n]));
+          for (int n = 0; n < 32; ++n) stg[n][fcol] = gelu_bf16(__uint_as_float(g[n]));
         } else {
           tmem_ld_wait();
-          // lane n holds the routing of row c0 + n; broadcast per column
+          // lane n holds the top-k weight of row c0 + n; broadcast per column.  Reference rounding
+          // points (combine_kernels.cu:191-197): bf16 GEMM output, fp32 product, bf16 row on the wire
           float my_scale = 0.f;
-          long long my_dst = -1;
-          if (c0 + lane < rows) {
-            my_scale = a.row_scale[row0 + c0 + lane];
-            my_dst = a.row_dst[row0 + c0 + lane];
-          }
+          if (c0 + lane < rows) my_scale = a.row_scale[row0 + c0 + lane];
 #pragma unroll
           for (int n = 0; n < 32; ++n) {
             const float sc = __shfl_sync(0xffffffffu, my_scale, n);
-            const long long dst = __shfl_sync(0xffffffffu, my_dst, n);
-            if (dst >= 0) {
-              // reference rounding points (combine_kernels.cu:191-197): bf16 GEMM output, fp32
-              // product with the top-k weight, bf16 row on the wire
-              const float v = bf16_round(__uint_as_float(g[n])) * sc;
-              __nv_bfloat16* out = a.staging != nullptr
-                                       ? a.staging + (size_t)(row0 + c0 + n) * a.w_rows_per_group
-                                       : a.panels[(int)(dst >> 40)] + (size_t)(dst & ((1ll << 40) - 1));
-              out[feat] = __float2bfloat16_rn(v);
-            }
+            stg[n][fcol] = __float2bfloat16_rn(bf16_round(__uint_as_float(g[n])) * sc);
           }
         }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        // write-out: warp ew owns rows ew*8 .. ew*8+7 of the chunk, two rows per instruction
+#pragma unroll
+        for (int rr = 0; rr < 4; ++rr) {
+          const int r = ew * 8 + rr * 2 + (lane >> 4);
+          if (c0 + r < rows) {
+            const uint4 v = *reinterpret_cast<const uint4*>(&stg[r][(lane & 15) * 8]);
+            __nv_bfloat16* out;
+            if (MODE != MODE_DOWN_COMBINE) {
+              out = a.act + (size_t)(row0 + c0 + r) * a.ld_act;
+            } else if (a.staging != nullptr) {
+              out = a.staging + (size_t)(row0 + c0 + r) * a.w_rows_per_group;
+            } else {
+              const long long dst = a.row_dst[row0 + c0 + r];
+              out = dst >= 0 ? a.panels[(int)(dst >> 40)] + (size_t)(dst & ((1ll << 40) - 1)) : nullptr;
+            }
+            if (out != nullptr) *reinterpret_cast<uint4*>(out + j * kTileM + (lane & 15) * 8) = v;
+          }
+        }
+        buf ^= 1;       // the next chunk stages into the other buffer; its barrier orders the reuse
       }
       tc_fence_before();
       __syncwarp();
@@ -338,8 +356,8 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
       // every source must have published its x for this step
       bool ok = true;
       if (a.x_flags != nullptr && lane < a.world) {
-        if (!wait_epoch_geq(a.x_flags + lane, a.epoch, a.flag_limit_ns)) {
-          record_timeout(a.status, WAIT_X, lane, (long long)a.epoch);
+        if (!wait_epoch_geq(a.x_flags + lane, epoch, a.flag_limit_ns)) {
+          record_timeout(a.status, WAIT_X, lane, (long long)epoch);
           ok = false;
         }
       }
@@ -355,7 +373,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         int base = 0;
         for (int ti = 0; ti < n_tiles; ++ti) {
           const int row0 = s_row0[ti];
-          const int rows = s_rows[ti];
+          const int rows = s_gr[ti] & 0x1FF;
           int first = (my_warp - base) % n_warps;
           if (first < 0) first += n_warps;
           base += rows;
@@ -364,7 +382,8 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             const int src = tok / a.tokens_per_rank;
             const int t = tok - src * a.tokens_per_rank;
             if (tok >= 0 && src < a.world) {
-              const __nv_bfloat16* xb = (src == a.rank && a.x_self != nullptr) ? a.x_self : a.x_ptrs[src];
+              const __nv_bfloat16* xb = (src == a.rank && a.x_self != nullptr)
+                                            ? a.x_self : ((epoch & 1) ? a.x_ptrs_odd[src] : a.x_ptrs[src]);
               const uint4* sp = reinterpret_cast<const uint4*>(xb + (size_t)t * a.k_extent);
               uint4* dp = reinterpret_cast<uint4*>(a.recv + (size_t)(row0 + r) * a.k_extent);
               for (int v0 = 0; v0 < vec_per_row; v0 += 32 * 8) {
@@ -407,7 +426,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
       const unsigned int prev = atomicInc(a.cta_counter, gridDim.x - 1);
       if (prev == gridDim.x - 1) {
         __threadfence_system();
-        for (int p = 0; p < a.world; ++p) st_release_sys(a.done_flags[p] + a.rank, a.epoch);
+        for (int p = 0; p < a.world; ++p) st_release_sys(a.done_flags[p] + a.rank, epoch);
       }
     }
   }

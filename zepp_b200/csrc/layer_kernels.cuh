@@ -9,8 +9,11 @@
 namespace zepp {
 
 // x [S, H] -> this rank's symmetric buffer, then `epoch` into every rank's x_flags[rank].
-__global__ void publish_x_kernel(const uint4* __restrict__ x, uint4* __restrict__ xsym, size_t n_vec, int rank,
-                                 int world, PeerTable flags, unsigned long long epoch, unsigned int* counter) {
+__global__ void publish_x_kernel(const uint4* __restrict__ x, uint4* __restrict__ xsym_even,
+                                 uint4* __restrict__ xsym_odd, size_t n_vec, int rank, int world, PeerTable flags,
+                                 const unsigned long long* epoch_ptr, unsigned int* counter) {
+  const unsigned long long epoch = step_epoch(epoch_ptr, false);
+  uint4* xsym = (epoch & 1) ? xsym_odd : xsym_even;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (size_t)gridDim.x * blockDim.x)
     xsym[i] = x[i];
   __threadfence_system();
@@ -29,7 +32,8 @@ struct MoveArgs {
   const int* m_this;                       // [2] rows, first global row
   const int* row_tok;                      // [cap]
   const long long* row_dst;                // [cap]
-  const __nv_bfloat16* const* x_ptrs;      // [W] symmetric x buffers
+  const __nv_bfloat16* const* x_ptrs;      // [W] symmetric x buffers (even epochs)
+  const __nv_bfloat16* const* x_ptrs_odd;  // (odd epochs)
   const __nv_bfloat16* x_self;             // this rank's x (read directly)
   __nv_bfloat16* recv;                     // [cap, H]
   const __nv_bfloat16* staging;            // [cap, H]
@@ -38,7 +42,8 @@ struct MoveArgs {
   const unsigned long long* x_flags;       // [W]
   unsigned int* counter;
   int H, S, world, rank, recv_cap;
-  unsigned long long epoch, limit_ns;
+  const unsigned long long* epoch_ptr;
+  unsigned long long limit_ns;
   unsigned long long* status;
 };
 
@@ -60,7 +65,8 @@ __device__ __forceinline__ void copy_row_warp(const uint4* sp, uint4* dp, int ve
 
 // recv[r] = x of row r's source token, pulled over NVLink (one warp per row).
 __global__ void dispatch_pull_kernel(MoveArgs a) {
-  if (!block_wait_all(a.x_flags, a.world, a.epoch, a.limit_ns, a.status, WAIT_X)) return;
+  const unsigned long long epoch = step_epoch(a.epoch_ptr, false);
+  if (!block_wait_all(a.x_flags, a.world, epoch, a.limit_ns, a.status, WAIT_X)) return;
   if (a.status[ST_VIOLATION] != 0ull) return;
   const int m = min(a.m_this[0], a.recv_cap);
   const int lane = threadIdx.x & 31;
@@ -70,7 +76,8 @@ __global__ void dispatch_pull_kernel(MoveArgs a) {
     const int src = tok / a.S;
     const int t = tok - src * a.S;
     if (tok < 0 || src >= a.world) continue;
-    const __nv_bfloat16* base = (src == a.rank && a.x_self != nullptr) ? a.x_self : a.x_ptrs[src];
+    const __nv_bfloat16* base = (src == a.rank && a.x_self != nullptr)
+                                    ? a.x_self : ((epoch & 1) ? a.x_ptrs_odd[src] : a.x_ptrs[src]);
     copy_row_warp(reinterpret_cast<const uint4*>(base + (size_t)t * a.H),
                   reinterpret_cast<uint4*>(a.recv + (size_t)r * a.H), a.H / 8, lane);
   }
@@ -78,6 +85,7 @@ __global__ void dispatch_pull_kernel(MoveArgs a) {
 
 // staging[r] -> the home rank's slot panel, then the completion epoch to every rank.
 __global__ void combine_push_kernel(MoveArgs a) {
+  const unsigned long long epoch = step_epoch(a.epoch_ptr, false);
   const int m = a.status[ST_VIOLATION] != 0ull ? 0 : min(a.m_this[0], a.recv_cap);
   const int lane = threadIdx.x & 31;
   const int wpb = blockDim.x >> 5;
@@ -94,7 +102,7 @@ __global__ void combine_push_kernel(MoveArgs a) {
     const unsigned int prev = atomicInc(a.counter, gridDim.x - 1);
     if (prev == gridDim.x - 1) {
       __threadfence_system();
-      for (int p = 0; p < a.world; ++p) st_release_sys(a.done_flags[p] + a.rank, a.epoch);
+      for (int p = 0; p < a.world; ++p) st_release_sys(a.done_flags[p] + a.rank, epoch);
     }
   }
 }
@@ -102,8 +110,9 @@ __global__ void combine_push_kernel(MoveArgs a) {
 // y[t] = bf16( sum_k float(panel[t, k]) ), once every rank's combine rows have landed.
 __global__ void combine_reduce_kernel(const __nv_bfloat16* __restrict__ panel, __nv_bfloat16* __restrict__ y, int S,
                                       int K, int H, const unsigned long long* done_flags, int world,
-                                      unsigned long long epoch, unsigned long long limit_ns,
+                                      const unsigned long long* epoch_ptr, unsigned long long limit_ns,
                                       unsigned long long* status) {
+  const unsigned long long epoch = step_epoch(epoch_ptr, false);
   if (!block_wait_all(done_flags, world, epoch, limit_ns, status, WAIT_COMBINE)) return;
   const int vec_per_row = H / 8;
   const size_t total = (size_t)S * vec_per_row;

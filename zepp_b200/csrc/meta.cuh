@@ -26,6 +26,7 @@ constexpr int kTileRowsMax = 128;
 struct MetaArgs {
   // input: either the gathered routing rows [R, 2*SK] (phys | weight bits) or vce directly
   const int* gathered;
+  const int* gathered_odd;  // odd-epoch copy when `epoch_ptr` is set
   const int* vce_in;
   int R, L, S, K, nlp, gpe, my_rank;
   int tokens_per_tile, tiles_per_src;
@@ -62,16 +63,22 @@ struct MetaArgs {
   const int* group_order;   // [gpe] schedule word per group (bit 30 = moved-in slot: its tiles go last) or nullptr
   // exchange wait
   const unsigned long long* routing_flags;
-  unsigned long long epoch, limit_ns;
+  const unsigned long long* epoch_ptr;
+  unsigned long long limit_ns;
   unsigned long long* status;
+  unsigned int* block_counter;   // pass1: the last block to finish runs the scan
 };
+
+__device__ void meta_scan_body(MetaArgs& a, int* chunks);
 
 __global__ void __launch_bounds__(kMetaThreads) meta_pass1_kernel(MetaArgs a) {
   extern __shared__ int sm[];
   const int R = a.R, NN = a.R / a.L, E_virt = a.R * a.gpe, SK = a.S * a.K;
   int* hist = sm;                       // [E_virt]
   int* ucs = sm + E_virt;               // [R + NN]
-  if (!block_wait_all(a.routing_flags, R, a.epoch, a.limit_ns, a.status, WAIT_ROUTING)) return;
+  const unsigned long long epoch = step_epoch(a.epoch_ptr, false);
+  if (a.epoch_ptr != nullptr && (epoch & 1)) a.gathered = a.gathered_odd;
+  if (!block_wait_all(a.routing_flags, R, epoch, a.limit_ns, a.status, WAIT_ROUTING)) return;
   const int src = blockIdx.x / a.tiles_per_src;
   const int tb = blockIdx.x - src * a.tiles_per_src;
   for (int i = threadIdx.x; i < E_virt + R + NN; i += blockDim.x) sm[i] = 0;
@@ -115,6 +122,15 @@ __global__ void __launch_bounds__(kMetaThreads) meta_pass1_kernel(MetaArgs a) {
   for (int e = threadIdx.x; e < E_virt; e += blockDim.x) th[e] = hist[e];
   int* tu = a.tile_uc + (size_t)blockIdx.x * (R + NN);
   for (int i = threadIdx.x; i < R + NN; i += blockDim.x) tu[i] = ucs[i];
+  // the last block to finish turns the per-tile counts into the step's tables (no extra launch)
+  __shared__ int is_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) is_last = atomicInc(a.block_counter, gridDim.x - 1) == gridDim.x - 1 ? 1 : 0;
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  meta_scan_body(a, sm);
 }
 
 // Exact demands of a step (python/zepp/capacity.py:30-55) from chunks[s][d] (rows from source s to
@@ -208,8 +224,8 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* warp_tot, int* t
   return warp_tot[wid] + incl - v;
 }
 
-__global__ void __launch_bounds__(kMetaThreads) meta_scan_kernel(MetaArgs a) {
-  extern __shared__ int chunks[];        // [R*R] rows from source s to destination rank d
+// chunks: shared memory [R*R], rows from source s to destination rank d
+__device__ void meta_scan_body(MetaArgs& a, int* chunks) {
   const int R = a.R, NN = a.R / a.L, E_virt = a.R * a.gpe, ucw = R + NN;
   const int n_blocks = R * a.tiles_per_src;
   __shared__ int warp_tot[33];

@@ -40,15 +40,27 @@ struct PeerTable {
   void* ptr[kMaxRanks];
 };
 
+// Step epoch.  A layer keeps a device-resident step counter so that a whole step can be replayed
+// as a CUDA graph with unchanged kernel arguments.  The first kernel of a step works under epoch
+// *ctr + 1 and its last block commits it; every later kernel of the step reads *ctr.  Buffers that
+// are double-buffered by step parity are passed as pairs and selected with (epoch & 1).
+__device__ __forceinline__ unsigned long long step_epoch(const unsigned long long* ctr, bool first) {
+  if (ctr == nullptr) return 0ull;
+  const unsigned long long v = *reinterpret_cast<const volatile unsigned long long*>(ctr);
+  return first ? v + 1 : v;
+}
+
 // ---------------------------------------------------------------------------------------
 // loads: d_own[G] = bincount(topk_own) and its publication to every rank
 // (python/zepp/planner.py:104-112: index_add_ + all_gather_into_tensor).
 // One block.  dst.ptr[p] is rank p's loads table [R, G]; flags.ptr[p] its arrival words [R].
 // ---------------------------------------------------------------------------------------
 __global__ void loads_publish_kernel(const int* __restrict__ topk_own, int n_entries, int G, int rank, int world,
-                                     PeerTable dst, PeerTable flags, unsigned long long epoch,
+                                     PeerTable dst0, PeerTable dst1, PeerTable flags, unsigned long long* ctr,
                                      unsigned long long* status, long long* route_stats) {
   extern __shared__ int hist[];
+  const unsigned long long epoch = step_epoch(ctr, true);      // first kernel of a step
+  const PeerTable& dst = (epoch & 1) ? dst1 : dst0;
   if (route_stats != nullptr && threadIdx.x < 4) route_stats[threadIdx.x] = 0;
   for (int g = threadIdx.x; g < G; g += blockDim.x) hist[g] = 0;
   __syncthreads();
@@ -66,6 +78,7 @@ __global__ void loads_publish_kernel(const int* __restrict__ topk_own, int n_ent
   __syncthreads();
   if (threadIdx.x < world && flags.ptr[threadIdx.x] != nullptr)
     st_release_sys(reinterpret_cast<unsigned long long*>(flags.ptr[threadIdx.x]) + rank, epoch);
+  if (threadIdx.x == 0 && ctr != nullptr) *ctr = epoch;
 }
 
 // Thread 0 of a block waits until every rank's word in `flags` reached `epoch`.
@@ -100,6 +113,7 @@ struct RouteArgs {
   const int* topk_own;      // [S*K]
   int n_entries;
   const int* loads;         // [R, G]
+  const int* loads_odd;     // the odd-epoch copy of the table when `epoch_ptr` is set (else unused)
   const int* l2p;           // [G, R]
   const int* lcnts;         // [G]
   int G, R, L, nlp, my_rank;
@@ -107,14 +121,16 @@ struct RouteArgs {
   int* ws;
   int* phys_own;            // [S*K]
   const unsigned long long* loads_flags;   // [R] or nullptr
-  unsigned long long epoch;
+  const unsigned long long* epoch_ptr;     // device step counter or nullptr (stand-alone use)
   unsigned long long limit_ns;
   unsigned long long* status;
   long long* stats;         // [4]: 0 stranded rows, 1 vacate moves, 2 ordinal overflow, 3 unused
 };
 
 __global__ void __launch_bounds__(256) route_kernel(RouteArgs a) {
-  if (!block_wait_all(a.loads_flags, a.R, a.epoch, a.limit_ns, a.status, WAIT_LOADS)) return;
+  const unsigned long long epoch = step_epoch(a.epoch_ptr, false);
+  if (a.epoch_ptr != nullptr && (epoch & 1)) a.loads = a.loads_odd;
+  if (!block_wait_all(a.loads_flags, a.R, epoch, a.limit_ns, a.status, WAIT_LOADS)) return;
   const int warps_per_block = blockDim.x >> 5;
   const int wib = threadIdx.x >> 5;
   const int g = blockIdx.x * warps_per_block + wib;
@@ -316,9 +332,10 @@ struct FinishArgs {
   int* ws;
   int* send_row;           // [2*S*K] local copy of the row (may be nullptr)
   PeerTable dst;           // rank p's gather table [R, 2*S*K]; nullptr entries skipped
+  PeerTable dst_odd;       // the odd-epoch tables
   PeerTable flags;         // rank p's arrival words [R]
   int world;               // ranks to publish to (0: none)
-  unsigned long long epoch;
+  const unsigned long long* epoch_ptr;
   unsigned int* block_counter;
   unsigned long long* status;
   long long* stats;
@@ -418,12 +435,14 @@ __global__ void route_vacate_kernel(FinishArgs a) {
 
 __global__ void route_finish_kernel(FinishArgs a) {
   const int SK = a.S * a.K;
+  const unsigned long long epoch = step_epoch(a.epoch_ptr, false);
+  const PeerTable& dst = (epoch & 1) ? a.dst_odd : a.dst;
   const int* wbits = reinterpret_cast<const int*>(a.probs_own);
   for (int n = blockIdx.x * blockDim.x + threadIdx.x; n < 2 * SK; n += gridDim.x * blockDim.x) {
     const int v = n < SK ? a.phys_own[n] : wbits[n - SK];
     if (a.send_row) a.send_row[n] = v;
     for (int p = 0; p < a.world; ++p)
-      if (a.dst.ptr[p]) reinterpret_cast<int*>(a.dst.ptr[p])[(size_t)a.my_rank * 2 * SK + n] = v;
+      if (dst.ptr[p]) reinterpret_cast<int*>(dst.ptr[p])[(size_t)a.my_rank * 2 * SK + n] = v;
   }
   __threadfence_system();
   __syncthreads();
@@ -432,7 +451,68 @@ __global__ void route_finish_kernel(FinishArgs a) {
     if (prev == gridDim.x - 1) {
       __threadfence_system();
       for (int p = 0; p < a.world; ++p)
-        if (a.flags.ptr[p]) st_release_sys(reinterpret_cast<unsigned long long*>(a.flags.ptr[p]) + a.my_rank, a.epoch);
+        if (a.flags.ptr[p]) st_release_sys(reinterpret_cast<unsigned long long*>(a.flags.ptr[p]) + a.my_rank, epoch);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Single-replica fast path: when no expert has more than one instance (every one-node
+// topology: the placement caps replicas at one per node) the water-fill is the identity --
+// every copy of expert g goes to its only slot -- and neither the tables nor the gathered loads
+// have a consumer (unless the swap decision wants the loads).  One kernel: phys = first valid
+// l2p entry of the copy's expert, send row [phys | weight bits] into every rank's gather table,
+// epoch flag by the last block.  It is the first kernel of the step when the loads exchange is
+// skipped (first = 1) and then commits the step counter.
+// ---------------------------------------------------------------------------------------
+struct SimpleRouteArgs {
+  const int* topk_own;
+  const float* probs_own;
+  const int* l2p;
+  const int* lcnts;
+  int SK, G, R, my_rank, world, first;
+  int* phys_own;
+  int* send_row;
+  PeerTable dst, dst_odd, flags;
+  unsigned long long* ctr;
+  unsigned int* block_counter;
+  unsigned long long* status;
+};
+
+__global__ void __launch_bounds__(256) route_simple_publish_kernel(SimpleRouteArgs a) {
+  const unsigned long long epoch = step_epoch(a.ctr, a.first != 0);
+  const PeerTable& dst = (epoch & 1) ? a.dst_odd : a.dst;
+  const int* wbits = reinterpret_cast<const int*>(a.probs_own);
+  for (int n = blockIdx.x * blockDim.x + threadIdx.x; n < a.SK; n += gridDim.x * blockDim.x) {
+    const int e = a.topk_own[n];
+    int p0 = 0;
+    if (e >= 0 && e < a.G) {
+      const int cnt = min(a.lcnts[e], a.R);
+      int j = 0;
+      while (j < cnt && a.l2p[e * a.R + j] < 0) ++j;
+      if (j < cnt) p0 = a.l2p[e * a.R + j];
+      else if (a.status) atomicOr(a.status + ST_ERROR, (unsigned long long)ERR_ROUTE);
+    } else if (a.status) {
+      atomicOr(a.status + ST_ERROR, (unsigned long long)ERR_BAD_INDEX);
+    }
+    const int wb = wbits[n];
+    a.phys_own[n] = p0;
+    if (a.send_row) { a.send_row[n] = p0; a.send_row[a.SK + n] = wb; }
+    for (int p = 0; p < a.world; ++p) {
+      int* row = reinterpret_cast<int*>(dst.ptr[p]) + (size_t)a.my_rank * 2 * a.SK;
+      row[n] = p0;
+      row[a.SK + n] = wb;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicInc(a.block_counter, gridDim.x - 1);
+    if (prev == gridDim.x - 1) {
+      __threadfence_system();
+      for (int p = 0; p < a.world; ++p)
+        st_release_sys(reinterpret_cast<unsigned long long*>(a.flags.ptr[p]) + a.my_rank, epoch);
+      if (a.first && a.ctr != nullptr) *a.ctr = epoch;
     }
   }
 }

@@ -42,6 +42,10 @@ static int fail(const char* fmt, ...) {
     if (_e != cudaSuccess) return fail("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__, __LINE__); \
   } while (0)
 
+static size_t meta_smem(int R, int NN, int E_virt);
+static size_t pass2_smem(int tokens_per_tile, int K, int E_virt);
+static int pass2_prepare(size_t bytes);
+
 extern "C" const char* zepp_last_error(void) { return g_err.c_str(); }
 extern "C" int zepp_abi_version(void) { return 1; }
 
@@ -228,7 +232,15 @@ struct zepp_layer {
   const void* x_self = nullptr;
   const int* ids_in = nullptr;
   const float* wts_in = nullptr;
-  bool pass2_attr = false;
+  unsigned long long* step_ctr = nullptr;     // device-resident step counter (epoch of the running step)
+  int c_max = 1;                              // largest replica count of the resident placement
+  bool use_graphs = true;
+  struct StepGraph {
+    const void *ids, *wts, *x, *y;
+    cudaGraphExec_t exec;
+    int64_t kernels;
+  };
+  std::vector<StepGraph> graphs;
 };
 
 static size_t al(size_t v) { return (v + 1023) / 1024 * 1024; }
@@ -315,6 +327,7 @@ static int layer_alloc(zepp_layer* l) {
   LA(l->row_scale, l->cap);
   LA(l->counters, 16);
   LA(l->status, ST_WORDS);
+  LA(l->step_ctr, 2);
   for (int b = 0; b < 2; ++b) LA(l->x_ptrs[b], R);
   LA(l->panels, R);
   LA(l->done_ptrs, R);
@@ -381,6 +394,8 @@ extern "C" int zepp_layer_create(zepp_rt* rt, const zepp_layer_cfg* c, zepp_laye
                              GemmCfg<MODE_SINGLE_GELU>::kSmemBytes));
   CU_OK(cudaFuncSetAttribute(moe_gemm_kernel<MODE_DOWN_COMBINE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              GemmCfg<MODE_DOWN_COMBINE>::kSmemBytes));
+  if (pass2_prepare(pass2_smem(l->tokens_per_tile, l->K, l->E_virt))) { delete l; return 1; }
+  if (meta_smem(l->W, l->NN, l->E_virt) > 48 * 1024) { delete l; return fail("too many ranks / experts for the metadata kernels"); }
   *out = l;
   return 0;
 }
@@ -389,6 +404,7 @@ extern "C" int zepp_layer_destroy(zepp_layer* l) {
   if (l) {
     cudaSetDevice(l->rt->device);
     cudaDeviceSynchronize();
+    for (auto& gph : l->graphs) cudaGraphExecDestroy(gph.exec);
     delete l;
   }
   return 0;
@@ -401,6 +417,10 @@ extern "C" int zepp_layer_set_placement(zepp_layer* l, const int32_t* p2l, const
   CU_OK(cudaMemcpyAsync(l->l2p, l2p, (size_t)l->G * l->W * 4, cudaMemcpyHostToDevice, st));
   CU_OK(cudaMemcpyAsync(l->lcnts, lcnts, (size_t)l->G * 4, cudaMemcpyHostToDevice, st));
   CU_OK(cudaStreamSynchronize(st));
+  l->c_max = 1;
+  for (int g = 0; g < l->G; ++g) l->c_max = lcnts[g] > l->c_max ? lcnts[g] : l->c_max;
+  for (auto& gph : l->graphs) cudaGraphExecDestroy(gph.exec);     // launch sequence may change with c_max
+  l->graphs.clear();
   l->have_placement = true;
   return 0;
 }
@@ -408,6 +428,8 @@ extern "C" int zepp_layer_set_placement(zepp_layer* l, const int32_t* p2l, const
 extern "C" int zepp_layer_set_weights(zepp_layer* l, const void* w1, const void* w2) {
   if (make_map(&l->tm_w1, w1, (uint64_t)l->gpe * l->ffn1, l->H, 128)) return 1;
   if (make_map(&l->tm_w2, w2, (uint64_t)l->gpe * l->H, l->I, 128)) return 1;
+  for (auto& gph : l->graphs) cudaGraphExecDestroy(gph.exec);     // the tensor maps are baked into captured launches
+  l->graphs.clear();
   l->have_weights = true;
   return 0;
 }
@@ -421,8 +443,8 @@ extern "C" int zepp_layer_set_weights(zepp_layer* l, const void* w1, const void*
 
 static MetaArgs layer_meta_args(zepp_layer* l) {
   MetaArgs m{};
-  const int b = (int)(l->epoch & 1);
-  m.gathered = l->xchg_all[b];
+  m.gathered = l->xchg_all[0];
+  m.gathered_odd = l->xchg_all[1];
   m.vce_in = nullptr;
   m.R = l->W; m.L = l->L; m.S = l->S; m.K = l->K; m.nlp = l->nlp; m.gpe = l->gpe; m.my_rank = l->rt->rank;
   m.tokens_per_tile = l->tokens_per_tile; m.tiles_per_src = l->tiles_per_src;
@@ -437,11 +459,15 @@ static MetaArgs layer_meta_args(zepp_layer* l) {
   m.row_tok = l->row_tok; m.row_dst = l->row_dst; m.row_scale = l->row_scale; m.hidden = l->H;
   m.group_order = nullptr;
   m.routing_flags = l->W > 1 ? l->routing_flags : nullptr;
-  m.epoch = l->epoch; m.limit_ns = l->rt->wait_ns; m.status = l->status;
+  m.epoch_ptr = l->step_ctr; m.limit_ns = l->rt->wait_ns; m.status = l->status;
+  m.block_counter = l->counters + 8;
   return m;
 }
 
-static size_t meta_smem(int R, int NN, int E_virt) { return (size_t)(E_virt + R + NN) * sizeof(int); }
+static size_t meta_smem(int R, int NN, int E_virt) {
+  const size_t a = (size_t)(E_virt + R + NN), b = (size_t)R * R;     // pass1 counters / the scan's chunk table
+  return (a > b ? a : b) * sizeof(int);
+}
 static size_t pass2_smem(int tokens_per_tile, int K, int E_virt) {
   return (size_t)((tokens_per_tile * K + 31) / 32) * E_virt * sizeof(int);
 }
@@ -455,36 +481,76 @@ static int pass2_prepare(size_t bytes) {
   return 0;
 }
 
+// Does this step need the gathered loads?  Only the water-fill (some expert has more than one
+// replica) and the swap decision consume them.
+static bool needs_loads(const zepp_layer* l) { return l->c_max > 1 || l->cfg.swap != 0; }
+
 extern "C" int zepp_layer_prepare_phase(zepp_layer* l, int phase, const int32_t* ids, const float* wts, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
   CU_OK(cudaSetDevice(l->rt->device));
   if (!l->have_placement) return fail("prepare: no placement set");
   const int R = l->W, me = l->rt->rank;
   if (phase == 0) {
-    l->epoch += 1;
-    const int b = (int)(l->epoch & 1);
+    l->epoch += 1;                 // host mirror of the device step counter
     // the routing inputs are read in place by this step's kernels (stream order keeps them valid)
     l->ids_in = ids;
     l->wts_in = wts;
-    loads_publish_kernel<<<1, 1024, l->G * sizeof(int), st>>>(ids, l->SK, l->G, me, R, l->loads_dst[b],
-                                                             l->loads_flag_dst, l->epoch, l->status, l->route_stats);
-    LAUNCH_OK();
+    if (needs_loads(l)) {
+      loads_publish_kernel<<<1, 1024, l->G * sizeof(int), st>>>(ids, l->SK, l->G, me, R, l->loads_dst[0], l->loads_dst[1],
+                                                               l->loads_flag_dst, l->step_ctr, l->status, l->route_stats);
+      LAUNCH_OK();
+    }
     return 0;
   }
-  const int b = (int)(l->epoch & 1);
   if (phase == 1) {
-    RouteArgs ra{};
     if (ids) { l->ids_in = ids; l->wts_in = wts; }
-    ra.topk_own = l->ids_in; ra.n_entries = l->SK; ra.loads = l->loads_all[b]; ra.l2p = l->l2p; ra.lcnts = l->lcnts;
-    ra.G = l->G; ra.R = R; ra.L = l->L; ra.nlp = l->nlp; ra.my_rank = me;
-    ra.c_num = l->cfg.c_num; ra.c_den = l->cfg.c_den; ra.ws = l->route_ws; ra.phys_own = l->phys_own;
-    ra.loads_flags = R > 1 ? l->loads_flags : nullptr;
-    ra.epoch = l->epoch; ra.limit_ns = l->rt->wait_ns; ra.status = l->status; ra.stats = l->route_stats;
-    route_kernel<<<(l->G + 7) / 8, 256, 0, st>>>(ra);
-    LAUNCH_OK();
+    if (l->c_max <= 1) {
+      SimpleRouteArgs sa{};
+      sa.topk_own = l->ids_in; sa.probs_own = l->wts_in; sa.l2p = l->l2p; sa.lcnts = l->lcnts;
+      sa.SK = l->SK; sa.G = l->G; sa.R = R; sa.my_rank = me; sa.world = R; sa.first = needs_loads(l) ? 0 : 1;
+      sa.phys_own = l->phys_own; sa.send_row = l->send_row; sa.dst = l->xchg_dst[0]; sa.dst_odd = l->xchg_dst[1];
+      sa.flags = l->routing_flag_dst; sa.ctr = l->step_ctr; sa.block_counter = l->counters + 0; sa.status = l->status;
+      if (l->cfg.swap) {
+        // the decision reads the gathered loads: wait for them with the generic router's table pass
+        RouteArgs ra{};
+        ra.topk_own = nullptr; ra.n_entries = 0; ra.loads = l->loads_all[0]; ra.loads_odd = l->loads_all[1];
+        ra.l2p = l->l2p; ra.lcnts = l->lcnts; ra.G = l->G; ra.R = R; ra.L = l->L; ra.nlp = l->nlp; ra.my_rank = me;
+        ra.c_num = l->cfg.c_num; ra.c_den = l->cfg.c_den; ra.ws = l->route_ws; ra.phys_own = l->phys_own;
+        ra.loads_flags = R > 1 ? l->loads_flags : nullptr; ra.epoch_ptr = l->step_ctr; ra.limit_ns = l->rt->wait_ns;
+        ra.status = l->status; ra.stats = l->route_stats;
+        route_kernel<<<(l->G + 7) / 8, 256, 0, st>>>(ra);
+        LAUNCH_OK();
+      }
+      route_simple_publish_kernel<<<(l->SK + 1023) / 1024, 256, 0, st>>>(sa);
+      LAUNCH_OK();
+    } else {
+      RouteArgs ra{};
+      ra.topk_own = l->ids_in; ra.n_entries = l->SK; ra.loads = l->loads_all[0]; ra.loads_odd = l->loads_all[1];
+      ra.l2p = l->l2p; ra.lcnts = l->lcnts;
+      ra.G = l->G; ra.R = R; ra.L = l->L; ra.nlp = l->nlp; ra.my_rank = me;
+      ra.c_num = l->cfg.c_num; ra.c_den = l->cfg.c_den; ra.ws = l->route_ws; ra.phys_own = l->phys_own;
+      ra.loads_flags = R > 1 ? l->loads_flags : nullptr;
+      ra.epoch_ptr = l->step_ctr; ra.limit_ns = l->rt->wait_ns; ra.status = l->status; ra.stats = l->route_stats;
+      route_kernel<<<(l->G + 7) / 8, 256, 0, st>>>(ra);
+      LAUNCH_OK();
+      FinishArgs fa{};
+      fa.topk_own = l->ids_in; fa.phys_own = l->phys_own; fa.probs_own = l->wts_in;
+      fa.S = l->S; fa.K = l->K; fa.G = l->G; fa.R = R; fa.L = l->L; fa.nlp = l->nlp; fa.my_rank = me;
+      fa.ws = l->route_ws; fa.send_row = l->send_row; fa.dst = l->xchg_dst[0]; fa.dst_odd = l->xchg_dst[1];
+      fa.flags = l->routing_flag_dst;
+      fa.world = R; fa.epoch_ptr = l->step_ctr; fa.block_counter = l->counters + 0; fa.status = l->status;
+      fa.stats = l->route_stats;
+      if (l->NN > 1) {
+        route_vacate_kernel<<<1, 32, 0, st>>>(fa);
+        LAUNCH_OK();
+      }
+      route_finish_kernel<<<8, 256, 0, st>>>(fa);
+      LAUNCH_OK();
+    }
     if (l->cfg.swap) {
       // decision + lane metadata on scratch copies of the tables (the decision is reported in the
       // result block; the resident placement changes only through zepp_layer_set_placement)
+      const int b = (int)(l->epoch & 1);
       CU_OK(cudaMemcpyAsync(l->p2l_try, l->p2l, (size_t)R * l->nlp * 4, cudaMemcpyDeviceToDevice, st));
       CU_OK(cudaMemcpyAsync(l->l2p_try, l->l2p, (size_t)l->G * R * 4, cudaMemcpyDeviceToDevice, st));
       const double C = (double)l->cfg.c_num / (double)l->cfg.c_den;
@@ -498,31 +564,14 @@ extern "C" int zepp_layer_prepare_phase(zepp_layer* l, int phase, const int32_t*
         return 1;
       l->launches++;
     }
-    FinishArgs fa{};
-    fa.topk_own = l->ids_in; fa.phys_own = l->phys_own; fa.probs_own = l->wts_in;
-    fa.S = l->S; fa.K = l->K; fa.G = l->G; fa.R = R; fa.L = l->L; fa.nlp = l->nlp; fa.my_rank = me;
-    fa.ws = l->route_ws; fa.send_row = l->send_row; fa.dst = l->xchg_dst[b]; fa.flags = l->routing_flag_dst;
-    fa.world = R; fa.epoch = l->epoch; fa.block_counter = l->counters + 0; fa.status = l->status;
-    fa.stats = l->route_stats;
-    if (l->NN > 1) {
-      route_vacate_kernel<<<1, 32, 0, st>>>(fa);
-      LAUNCH_OK();
-    }
-    route_finish_kernel<<<8, 256, 0, st>>>(fa);
-    LAUNCH_OK();
     return 0;
   }
   if (phase == 2) {
     MetaArgs m = layer_meta_args(l);
     const int grid = R * l->tiles_per_src;
-    const size_t sm = meta_smem(R, l->NN, l->E_virt);
-    const size_t sm2 = pass2_smem(l->tokens_per_tile, l->K, l->E_virt);
-    if (pass2_prepare(sm2)) return 1;
-    meta_pass1_kernel<<<grid, kMetaThreads, sm, st>>>(m);
+    meta_pass1_kernel<<<grid, kMetaThreads, meta_smem(R, l->NN, l->E_virt), st>>>(m);      // + scan in its last block
     LAUNCH_OK();
-    meta_scan_kernel<<<1, kMetaThreads, (size_t)R * R * sizeof(int), st>>>(m);
-    LAUNCH_OK();
-    meta_pass2_kernel<<<grid, kMetaThreads, sm2, st>>>(m);
+    meta_pass2_kernel<<<grid, kMetaThreads, pass2_smem(l->tokens_per_tile, l->K, l->E_virt), st>>>(m);
     LAUNCH_OK();
     return 0;
   }
@@ -545,8 +594,9 @@ static GemmArgs layer_gemm_args(zepp_layer* l, bool first) {
   g.act = l->act; g.ld_act = l->I;
   g.row_scale = l->row_scale; g.row_dst = l->row_dst; g.panels = l->panels; g.staging = nullptr;
   g.done_flags = nullptr; g.cta_counter = l->counters + 2;
-  g.world = l->W; g.rank = l->rt->rank; g.epoch = l->epoch;
-  g.row_tok = l->row_tok; g.x_ptrs = l->x_ptrs[l->epoch & 1]; g.x_self = (const __nv_bfloat16*)l->x_self;
+  g.world = l->W; g.rank = l->rt->rank; g.epoch_ptr = l->step_ctr;
+  g.row_tok = l->row_tok; g.x_ptrs = l->x_ptrs[0]; g.x_ptrs_odd = l->x_ptrs[1];
+  g.x_self = (const __nv_bfloat16*)l->x_self;
   g.x_flags = l->W > 1 ? l->x_flags : nullptr;
   g.recv = l->recv; g.tile_ready = l->tile_ready; g.tokens_per_rank = l->S; g.gather = 0;
   g.status = l->status; g.mbar_limit = 1u << 24; g.flag_limit_ns = l->rt->wait_ns;
@@ -573,11 +623,11 @@ static int launch_gemm(zepp_layer* l, const CUtensorMap& tw, const CUtensorMap* 
 static MoveArgs layer_move_args(zepp_layer* l) {
   MoveArgs m{};
   m.m_this = l->m_this; m.row_tok = l->row_tok; m.row_dst = l->row_dst;
-  m.x_ptrs = l->x_ptrs[l->epoch & 1]; m.x_self = (const __nv_bfloat16*)l->x_self;
+  m.x_ptrs = l->x_ptrs[0]; m.x_ptrs_odd = l->x_ptrs[1]; m.x_self = (const __nv_bfloat16*)l->x_self;
   m.recv = l->recv; m.staging = l->staging; m.panels = l->panels; m.done_flags = l->done_ptrs;
   m.x_flags = l->W > 1 ? l->x_flags : nullptr; m.counter = l->counters + 4;
   m.H = l->H; m.S = l->S; m.world = l->W; m.rank = l->rt->rank; m.recv_cap = l->cap;
-  m.epoch = l->epoch; m.limit_ns = l->rt->wait_ns; m.status = l->status;
+  m.epoch_ptr = l->step_ctr; m.limit_ns = l->rt->wait_ns; m.status = l->status;
   return m;
 }
 
@@ -587,13 +637,12 @@ extern "C" int zepp_layer_forward_phase(zepp_layer* l, int phase, const void* x,
   if (!l->have_weights) return fail("forward: no weights set");
   if (l->epoch == 0) return fail("forward: prepare has not run");
   const bool direct = l->cfg.strategy == 1;
-  const int b = (int)(l->epoch & 1);
   if (phase == 0) {
     l->x_self = x;
     if (l->W > 1) {
       const size_t n_vec = (size_t)l->S * l->H / 8;
-      publish_x_kernel<<<64, 256, 0, st>>>((const uint4*)x, (uint4*)l->xsym[b], n_vec, l->rt->rank, l->W,
-                                          l->x_flag_dst, l->epoch, l->counters + 6);
+      publish_x_kernel<<<64, 256, 0, st>>>((const uint4*)x, (uint4*)l->xsym[0], (uint4*)l->xsym[1], n_vec, l->rt->rank,
+                                          l->W, l->x_flag_dst, l->step_ctr, l->counters + 6);
       LAUNCH_OK();
     }
     return 0;
@@ -628,7 +677,7 @@ extern "C" int zepp_layer_forward_phase(zepp_layer* l, int phase, const void* x,
   }
   if (phase == 3) {
     combine_reduce_kernel<<<l->rt->sm_count * 2, 256, 0, st>>>(l->panel, (__nv_bfloat16*)y, l->S, l->K, l->H,
-                                                            l->done_flags, l->W, l->epoch, l->rt->wait_ns, l->status);
+                                                            l->done_flags, l->W, l->step_ctr, l->rt->wait_ns, l->status);
     LAUNCH_OK();
     return 0;
   }
@@ -641,9 +690,71 @@ extern "C" int zepp_layer_forward(zepp_layer* l, const void* x, void* y, void* s
   return 0;
 }
 
+// One whole step in launch order.  x is published right after the first planning kernel, long before
+// the dispatch GEMM of any rank needs it, so the GEMM's wait for x never stalls on rank skew.
+static int step_enqueue(zepp_layer* l, const int32_t* ids, const float* wts, const void* x, void* y, void* stream) {
+  if (zepp_layer_prepare_phase(l, 0, ids, wts, stream)) return 1;
+  if (needs_loads(l)) {
+    if (zepp_layer_forward_phase(l, 0, x, y, stream)) return 1;
+    if (zepp_layer_prepare_phase(l, 1, ids, wts, stream)) return 1;
+  } else {
+    if (zepp_layer_prepare_phase(l, 1, ids, wts, stream)) return 1;     // commits the step counter
+    if (zepp_layer_forward_phase(l, 0, x, y, stream)) return 1;
+  }
+  if (zepp_layer_prepare_phase(l, 2, ids, wts, stream)) return 1;
+  for (int ph = 1; ph < 4; ++ph)
+    if (zepp_layer_forward_phase(l, ph, x, y, stream)) return 1;
+  return 0;
+}
+
+// prepare + forward as one call.  The launch sequence of a step depends only on the four
+// pointers (every count, offset and the epoch live in device memory), so it is captured once
+// per pointer set into a CUDA graph and replayed: one graph launch per step instead of 6-9
+// kernel launches.  Graphs are skipped with swap on (the lane metadata bakes the host epoch).
 extern "C" int zepp_layer_step(zepp_layer* l, const int32_t* ids, const float* wts, const void* x, void* y, void* stream) {
-  if (zepp_layer_prepare(l, ids, wts, stream)) return 1;
-  return zepp_layer_forward(l, x, y, stream);
+  cudaStream_t st = (cudaStream_t)stream;
+  CU_OK(cudaSetDevice(l->rt->device));
+  if (!l->have_weights) return fail("step: no weights set");
+  if (!l->use_graphs || l->cfg.swap) return step_enqueue(l, ids, wts, x, y, stream);
+  for (auto& gph : l->graphs) {
+    if (gph.ids == ids && gph.wts == wts && gph.x == x && gph.y == y) {
+      CU_OK(cudaGraphLaunch(gph.exec, st));
+      l->epoch += 1;
+      l->launches += gph.kernels;
+      l->x_self = x; l->ids_in = ids; l->wts_in = wts;
+      return 0;
+    }
+  }
+  if (l->graphs.size() >= 32) return step_enqueue(l, ids, wts, x, y, stream);
+  const int64_t before = l->launches;
+  const unsigned long long epoch_before = l->epoch;
+  cudaGraph_t graph = nullptr;
+  CU_OK(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+  const int rc = step_enqueue(l, ids, wts, x, y, stream);
+  cudaError_t e = cudaStreamEndCapture(st, &graph);
+  l->epoch = epoch_before;           // nothing ran yet: the capture only recorded the launches
+  const int64_t kernels = l->launches - before;
+  l->launches = before;
+  if (rc != 0 || e != cudaSuccess || graph == nullptr) {
+    if (graph) cudaGraphDestroy(graph);
+    cudaGetLastError();
+    l->use_graphs = false;           // fall back to plain launches for good
+    return step_enqueue(l, ids, wts, x, y, stream);
+  }
+  zepp_layer::StepGraph gph{};
+  gph.ids = ids; gph.wts = wts; gph.x = x; gph.y = y; gph.kernels = kernels;
+  e = cudaGraphInstantiate(&gph.exec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    l->use_graphs = false;
+    return step_enqueue(l, ids, wts, x, y, stream);
+  }
+  l->graphs.push_back(gph);
+  CU_OK(cudaGraphLaunch(gph.exec, st));
+  l->epoch += 1;
+  l->launches += kernels;
+  return 0;
 }
 
 extern "C" int zepp_layer_status(zepp_layer* l, void* stream, uint64_t out[8]) {
@@ -714,14 +825,14 @@ extern "C" int zepp_route(const int32_t* topk_own, int S, int K, const int32_t* 
   RouteArgs ra{};
   ra.topk_own = topk_own; ra.n_entries = S * K; ra.loads = loads; ra.l2p = l2p; ra.lcnts = lcnts;
   ra.G = G; ra.R = R; ra.L = L; ra.nlp = nlp; ra.my_rank = my_rank; ra.c_num = c_num; ra.c_den = c_den;
-  ra.ws = ws; ra.phys_own = phys_own; ra.loads_flags = nullptr; ra.epoch = 0; ra.limit_ns = 0; ra.status = nullptr;
+  ra.ws = ws; ra.phys_own = phys_own; ra.loads_flags = nullptr; ra.epoch_ptr = nullptr; ra.limit_ns = 0; ra.status = nullptr;
   ra.stats = (long long*)stats;
   if (stats) CU_OK(cudaMemsetAsync(stats, 0, 32, st));
   route_kernel<<<(G + 7) / 8, 256, 0, st>>>(ra);
   CU_OK(cudaGetLastError());
   FinishArgs fa{};
   fa.topk_own = topk_own; fa.phys_own = phys_own; fa.probs_own = probs_own; fa.S = S; fa.K = K; fa.G = G; fa.R = R;
-  fa.L = L; fa.nlp = nlp; fa.my_rank = my_rank; fa.ws = ws; fa.send_row = send_row; fa.world = 0; fa.epoch = 0;
+  fa.L = L; fa.nlp = nlp; fa.my_rank = my_rank; fa.ws = ws; fa.send_row = send_row; fa.world = 0; fa.epoch_ptr = nullptr;
   fa.status = nullptr; fa.stats = (long long*)stats;
   if (R / L > 1 && topk_own != nullptr) {
     route_vacate_kernel<<<1, 32, 0, st>>>(fa);
@@ -778,15 +889,17 @@ extern "C" int zepp_routed_meta(const int32_t* gathered, const int32_t* vce_in, 
   m.tile_hist = (int*)w; w += al(tiles * E_virt * 4);
   m.tile_uc = (int*)w; w += al(tiles * 2 * R * 4);
   m.expert_base = (int*)w;
-  m.n_tiles = nullptr; m.row_tok = nullptr; m.status = nullptr; m.routing_flags = nullptr;
+  m.n_tiles = nullptr; m.row_tok = nullptr; m.status = nullptr; m.routing_flags = nullptr; m.epoch_ptr = nullptr;
+  uint8_t* wend = (uint8_t*)m.expert_base + al((size_t)(E_virt + 1) * 4);
+  m.block_counter = (unsigned int*)wend;          // one self-resetting word at the end of the workspace
   const int grid = (int)tiles;
   const size_t sm = meta_smem(R, NN, E_virt);
   const size_t sm2 = pass2_smem(m.tokens_per_tile, K, E_virt);
   if (gpe > kMetaThreads) return fail("routed_meta: too many groups per rank");
+  if (sm > 48 * 1024) return fail("routed_meta: too many ranks / experts");
   if (pass2_prepare(sm2)) return 1;
+  CU_OK(cudaMemsetAsync(m.block_counter, 0, 4, st));
   meta_pass1_kernel<<<grid, kMetaThreads, sm, st>>>(m);
-  CU_OK(cudaGetLastError());
-  meta_scan_kernel<<<1, kMetaThreads, (size_t)R * R * sizeof(int), st>>>(m);
   CU_OK(cudaGetLastError());
   meta_pass2_kernel<<<grid, kMetaThreads, sm2, st>>>(m);
   CU_OK(cudaGetLastError());
@@ -882,9 +995,10 @@ extern "C" int zepp_routed_meta_noalloc(const int32_t* gathered, const int32_t* 
     }
     scratch = g_meta_scratch_addr[dev];
   }
-  // Nothing in the scratch has to start at zero: every word a kernel of this call reads (tile
-  // histograms, tile unique counts, expert bases) is written earlier in the same call, so the
-  // previous call's leftovers are harmless.
+  // The scratch keeps the previous call's contents.  The only word that has to start at zero (the
+  // block counter that elects the last metadata block) is cleared by zepp_routed_meta on the
+  // stream at the start of every call; every other word a kernel of this call reads (tile
+  // histograms, tile unique counts, expert bases) is written earlier in the same call.
   return zepp_routed_meta(gathered, vce_in, R, L, S, K, nlp, gpe, my_rank, direct, relay_slots, caps, copies_per_rank,
                           vce, probs_all, splits, scatter_index, sps, uc, demands, dplan, cplan, scratch, stream);
 }
