@@ -187,3 +187,32 @@ def test_bounded_wait_gives_up_and_context_survives():
     res = C.wait_geq(flag, 5, 20)
     assert int(res[0]) == 1
     assert float(torch.ones(4, device=DEV).sum()) == 4.0
+
+
+def test_capacities_against_golden(planner_cases, config_cases):
+    """Init-time capacity sizing through the device router == the reference's compute_capacities
+    (python/zepp/routing.py:400-458), on the small golden cases and on the full-size benchmark
+    routings including their swap orbits."""
+    from zepp_b200.placement import Placement
+    from zepp_b200.routing import compute_capacities
+    from zepp_b200.swap import swap_orbit
+    for i in range(0, planner_cases.n, 3):
+        c = planner_cases.case(i)
+        R, L, G, K, S, nlp, c_num, c_den = [int(v) for v in c["dims"]]
+        pl = Placement(torch.from_numpy(c["p2l"]), torch.from_numpy(c["l2p"]), torch.from_numpy(c["lcnts"]), {})
+        caps = compute_capacities(torch.from_numpy(c["topk"]), [pl], nlp, L, c_num / c_den, None)
+        assert caps.as_list() == c["caps"].tolist(), (i, caps.as_list(), c["caps"].tolist())
+    z = config_cases
+    for name in ("qwen30b_w8", "qwen235b_w4", "qwen235b_w8", "qwen235b_w8_l4", "k2_w8"):
+        W, L, G, K, S, nlp, zs, _ = [int(v) for v in z[f"{name}.dims"]]
+        topk = torch.from_numpy(z[f"{name}.topk"].astype(np.int32))
+        p2l = torch.from_numpy(z[f"{name}.p2l"])
+        from zepp_b200.placement import rebuild_l2p
+        lcnts = torch.bincount(p2l[p2l >= 0].long(), minlength=G).int()
+        pl = Placement(p2l, rebuild_l2p(p2l, G, W), lcnts, {})
+        placements = [pl]
+        if zs:
+            load_g = torch.bincount(topk.reshape(-1).long(), minlength=G)
+            placements += swap_orbit(load_g, pl, L, nlp, 0.25)
+        caps = compute_capacities(topk, placements, nlp, L, 0.25, None)
+        assert caps.as_list() == z[f"{name}.caps"].tolist(), (name, caps.as_list(), z[f"{name}.caps"].tolist())

@@ -235,6 +235,7 @@ struct zepp_layer {
   unsigned long long* step_ctr = nullptr;     // device-resident step counter (epoch of the running step)
   int c_max = 1;                              // largest replica count of the resident placement
   bool use_graphs = true;
+  cudaStream_t capture_stream = nullptr;
   struct StepGraph {
     const void *ids, *wts, *x, *y;
     cudaGraphExec_t exec;
@@ -405,6 +406,7 @@ extern "C" int zepp_layer_destroy(zepp_layer* l) {
     cudaSetDevice(l->rt->device);
     cudaDeviceSynchronize();
     for (auto& gph : l->graphs) cudaGraphExecDestroy(gph.exec);
+    if (l->capture_stream) cudaStreamDestroy(l->capture_stream);
     delete l;
   }
   return 0;
@@ -729,9 +731,16 @@ extern "C" int zepp_layer_step(zepp_layer* l, const int32_t* ids, const float* w
   const int64_t before = l->launches;
   const unsigned long long epoch_before = l->epoch;
   cudaGraph_t graph = nullptr;
-  CU_OK(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
-  const int rc = step_enqueue(l, ids, wts, x, y, stream);
-  cudaError_t e = cudaStreamEndCapture(st, &graph);
+  // recorded on a stream of the layer's own (the caller's may be the legacy default stream, which
+  // cannot capture); the instantiated graph is launched on the caller's stream
+  if (l->capture_stream == nullptr) CU_OK(cudaStreamCreateWithFlags(&l->capture_stream, cudaStreamNonBlocking));
+  if (cudaStreamBeginCapture(l->capture_stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+    cudaGetLastError();
+    l->use_graphs = false;
+    return step_enqueue(l, ids, wts, x, y, stream);
+  }
+  const int rc = step_enqueue(l, ids, wts, x, y, (void*)l->capture_stream);
+  cudaError_t e = cudaStreamEndCapture(l->capture_stream, &graph);
   l->epoch = epoch_before;           // nothing ran yet: the capture only recorded the launches
   const int64_t kernels = l->launches - before;
   l->launches = before;
