@@ -241,6 +241,9 @@ def main():
     layer.check()
     ms_total = max_over_ranks(t_begin.elapsed_time(t_end))
     ms_step = ms_total / args.steps
+    for i in range(3):
+        step_resident(i)
+    timeline = layer.trace()         # device-side stamps of the last graph-launched step
     # per-kernel brackets (the reference's marks): the same steps again, phase by phase, events between
     evs = [{n: ev() for n in names} for _ in range(args.steps)]
     barrier()
@@ -292,6 +295,7 @@ def main():
                    "l2": "expert weights streamed per step exceed the 126 MB L2 (inputs larger than L2)",
                    "timed": "prepare (device planning) + forward"},
         "latency_us": ms_step * 1e3,
+        "device_timeline_us": timeline,
         "breakdown_us": {"plan": plan_ms * 1e3, "dispatch_gemm": gemm1_ms * 1e3, "combine_gemm_reduce": comb_ms * 1e3},
         "roofline_layer": {"t_flop_us": t_flop * 1e6, "t_hbm_weights_us": t_hbm * 1e6,
                            "frac_of_3term": max(t_flop, t_hbm) / (ms_step * 1e-3), "rows_this_rank": m_r},

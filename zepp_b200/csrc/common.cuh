@@ -19,7 +19,10 @@ enum StatusWord : int {
   ST_WAIT_PEER = 2,    // peer / item index of the wait that gave up
   ST_WAIT_EPOCH = 3,   // epoch it waited for
   ST_VIOLATION = 4,    // capacity violation mask of the step (demands kernel)
-  ST_WORDS = 8
+  // device timeline of the last step (globaltimer ns), written by block 0 / the last block of each kernel
+  TR_ROUTE = 8, TR_PASS1 = 9, TR_PASS1_GO = 10, TR_PASS2 = 11, TR_GEMM1 = 12, TR_GEMM1_X = 13, TR_GEMM1_END = 14,
+  TR_GEMM2 = 15, TR_GEMM2_END = 16, TR_REDUCE = 17, TR_REDUCE_GO = 18, TR_REDUCE_END = 19,
+  ST_WORDS = 32
 };
 enum ErrorBit : unsigned long long {
   ERR_TIMEOUT = 1ull,        // a bounded wait ran out
@@ -37,6 +40,13 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
+}
+
+__device__ __forceinline__ void trace_mark(unsigned long long* status, int slot) {
+  if (status != nullptr) status[slot] = globaltimer_ns();
+}
+__device__ __forceinline__ void trace_mark_max(unsigned long long* status, int slot) {
+  if (status != nullptr) atomicMax(status + slot, globaltimer_ns());
 }
 
 __device__ __forceinline__ void record_timeout(unsigned long long* status, int what, long long peer,
@@ -57,6 +67,10 @@ __device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long
 }
 __device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
   asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+// epoch word store after the caller's own system-scope fence (one fence, then one store per peer)
+__device__ __forceinline__ void st_relaxed_sys(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 __device__ __forceinline__ unsigned int ld_acquire_gpu_u32(const unsigned int* p) {
   unsigned int v;

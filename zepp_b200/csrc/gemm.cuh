@@ -144,6 +144,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
   }
 
   if (threadIdx.x == 0) {
+    if (blockIdx.x == 0) trace_mark(a.status, MODE == MODE_DOWN_COMBINE ? TR_GEMM2 : TR_GEMM1);
     abort_flag = 0;
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -362,6 +363,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         }
       }
       ok = __all_sync(0xffffffffu, ok);
+      if (blockIdx.x == 0 && gw == 0 && lane == 0) trace_mark(a.status, TR_GEMM1_X);
       if (!ok) {
         if (lane == 0) abort_flag = 1;
       } else {
@@ -414,19 +416,20 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
   // ------------------------------------------------------------------ teardown
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) trace_mark_max(a.status, MODE == MODE_DOWN_COMBINE ? TR_GEMM2_END : TR_GEMM1_END);
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
   if (MODE == MODE_DOWN_COMBINE && a.done_flags != nullptr) {
-    // all of this CTA's panel stores are ordered before its arrival; the last CTA publishes the epoch
-    __threadfence_system();
-    __syncthreads();
+    // the block barrier above ordered every thread's panel stores before thread 0; its fence makes
+    // them visible system-wide before the CTA's arrival; the last CTA publishes the epoch
     if (threadIdx.x == 0) {
+      __threadfence_system();
       const unsigned int prev = atomicInc(a.cta_counter, gridDim.x - 1);
       if (prev == gridDim.x - 1) {
         __threadfence_system();
-        for (int p = 0; p < a.world; ++p) st_release_sys(a.done_flags[p] + a.rank, epoch);
+        for (int p = 0; p < a.world; ++p) st_relaxed_sys(a.done_flags[p] + a.rank, epoch);
       }
     }
   }

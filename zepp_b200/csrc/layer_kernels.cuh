@@ -16,14 +16,14 @@ __global__ void publish_x_kernel(const uint4* __restrict__ x, uint4* __restrict_
   uint4* xsym = (epoch & 1) ? xsym_odd : xsym_even;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (size_t)gridDim.x * blockDim.x)
     xsym[i] = x[i];
-  __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence_system();
     const unsigned int prev = atomicInc(counter, gridDim.x - 1);
     if (prev == gridDim.x - 1) {
       __threadfence_system();
       for (int p = 0; p < world; ++p)
-        st_release_sys(reinterpret_cast<unsigned long long*>(flags.ptr[p]) + rank, epoch);
+        st_relaxed_sys(reinterpret_cast<unsigned long long*>(flags.ptr[p]) + rank, epoch);
     }
   }
 }
@@ -96,13 +96,13 @@ __global__ void combine_push_kernel(MoveArgs a) {
     copy_row_warp(reinterpret_cast<const uint4*>(a.staging + (size_t)r * a.H),
                   reinterpret_cast<uint4*>(a.panels[home] + (size_t)(dst & ((1ll << 40) - 1))), a.H / 8, lane);
   }
-  __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence_system();
     const unsigned int prev = atomicInc(a.counter, gridDim.x - 1);
     if (prev == gridDim.x - 1) {
       __threadfence_system();
-      for (int p = 0; p < a.world; ++p) st_release_sys(a.done_flags[p] + a.rank, epoch);
+      for (int p = 0; p < a.world; ++p) st_relaxed_sys(a.done_flags[p] + a.rank, epoch);
     }
   }
 }
@@ -113,7 +113,9 @@ __global__ void combine_reduce_kernel(const __nv_bfloat16* __restrict__ panel, _
                                       const unsigned long long* epoch_ptr, unsigned long long limit_ns,
                                       unsigned long long* status) {
   const unsigned long long epoch = step_epoch(epoch_ptr, false);
+  if (blockIdx.x == 0 && threadIdx.x == 0) trace_mark(status, TR_REDUCE);
   if (!block_wait_all(done_flags, world, epoch, limit_ns, status, WAIT_COMBINE)) return;
+  if (blockIdx.x == 0 && threadIdx.x == 0) trace_mark(status, TR_REDUCE_GO);
   const int vec_per_row = H / 8;
   const size_t total = (size_t)S * vec_per_row;
   const bool dead = status[ST_VIOLATION] != 0ull;
@@ -122,14 +124,23 @@ __global__ void combine_reduce_kernel(const __nv_bfloat16* __restrict__ panel, _
     const int v = (int)(i - t * vec_per_row);
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     if (!dead) {
-      for (int k = 0; k < K; ++k) {
-        const uint4 raw = reinterpret_cast<const uint4*>(panel + ((size_t)t * K + k) * H)[v];
-        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      // eight independent 16-byte loads in flight per thread, then the fp32 adds in slot order
+      for (int k0 = 0; k0 < K; k0 += 8) {
+        uint4 raw[8];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const float2 f = __bfloat1622float2(h2[q]);
-          acc[2 * q] += f.x;
-          acc[2 * q + 1] += f.y;
+        for (int q = 0; q < 8; ++q)
+          if (k0 + q < K) raw[q] = reinterpret_cast<const uint4*>(panel + ((size_t)t * K + k0 + q) * H)[v];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          if (k0 + q < K) {
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[q]);
+#pragma unroll
+            for (int z = 0; z < 4; ++z) {
+              const float2 f = __bfloat1622float2(h2[z]);
+              acc[2 * z] += f.x;
+              acc[2 * z + 1] += f.y;
+            }
+          }
         }
       }
     }
@@ -139,6 +150,7 @@ __global__ void combine_reduce_kernel(const __nv_bfloat16* __restrict__ panel, _
     for (int q = 0; q < 4; ++q) o2[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
     reinterpret_cast<uint4*>(y + t * H)[v] = out;
   }
+  if (threadIdx.x == 0) trace_mark_max(status, TR_REDUCE_END);
 }
 
 }  // namespace zepp

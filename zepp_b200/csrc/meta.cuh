@@ -78,7 +78,9 @@ __global__ void __launch_bounds__(kMetaThreads) meta_pass1_kernel(MetaArgs a) {
   int* ucs = sm + E_virt;               // [R + NN]
   const unsigned long long epoch = step_epoch(a.epoch_ptr, false);
   if (a.epoch_ptr != nullptr && (epoch & 1)) a.gathered = a.gathered_odd;
+  if (blockIdx.x == 0 && threadIdx.x == 0) trace_mark(a.status, TR_PASS1);
   if (!block_wait_all(a.routing_flags, R, epoch, a.limit_ns, a.status, WAIT_ROUTING)) return;
+  if (blockIdx.x == 0 && threadIdx.x == 0) trace_mark(a.status, TR_PASS1_GO);
   const int src = blockIdx.x / a.tiles_per_src;
   const int tb = blockIdx.x - src * a.tiles_per_src;
   for (int i = threadIdx.x; i < E_virt + R + NN; i += blockDim.x) sm[i] = 0;
@@ -224,52 +226,66 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* warp_tot, int* t
   return warp_tot[wid] + incl - v;
 }
 
-// chunks: shared memory [R*R], rows from source s to destination rank d
-__device__ void meta_scan_body(MetaArgs& a, int* chunks) {
+// Shared memory of the scan (ints): chunks[R*R] (rows from source s to destination rank d) |
+// uc[R*(R+NN)] | splits[E_virt] | base[E_virt+1].  Everything later stages read comes from these
+// copies, so the block goes to global memory once to read the per-tile counts and once to write.
+__host__ __device__ inline size_t meta_scan_smem_ints(int R, int NN, int E_virt) {
+  return (size_t)R * R + (size_t)R * (R + NN) + 2 * (size_t)E_virt + 1;
+}
+
+__device__ void meta_scan_body(MetaArgs& a, int* sm) {
   const int R = a.R, NN = a.R / a.L, E_virt = a.R * a.gpe, ucw = R + NN;
   const int n_blocks = R * a.tiles_per_src;
+  int* chunks = sm;
+  int* s_uc = chunks + R * R;
+  int* s_splits = s_uc + R * ucw;
+  int* s_base = s_splits + E_virt;
   __shared__ int warp_tot[33];
   __shared__ long long viol;
-  // per source splits, totals
+  __syncthreads();
+  if (threadIdx.x == 0) trace_mark(a.status, 20);
+  for (int i = threadIdx.x; i < R * R; i += blockDim.x) chunks[i] = 0;
+  __syncthreads();
+  // per source splits, totals, chunk table
   for (int e = threadIdx.x; e < E_virt; e += blockDim.x) {
     int tot = 0;
+    const int d = e / a.gpe;
     for (int s = 0; s < R; ++s) {
       int acc = 0;
       for (int tb = 0; tb < a.tiles_per_src; ++tb) acc += a.tile_hist[(size_t)(s * a.tiles_per_src + tb) * E_virt + e];
       a.sps[s * E_virt + e] = acc;
+      if (acc) atomicAdd(&chunks[s * R + d], acc);
       tot += acc;
     }
     a.splits[e] = tot;
+    s_splits[e] = tot;
   }
   for (int i = threadIdx.x; i < R * ucw; i += blockDim.x) {
     const int s = i / ucw, d = i - s * ucw;
     int acc = 0;
     for (int tb = 0; tb < a.tiles_per_src; ++tb) acc += a.tile_uc[(size_t)(s * a.tiles_per_src + tb) * ucw + d];
     a.uc[i] = acc;
+    s_uc[i] = acc;
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < R * R; i += blockDim.x) {
-    const int s = i / R, d = i - s * R;
-    int acc = 0;
-    for (int e = 0; e < a.gpe; ++e) acc += a.sps[s * E_virt + d * a.gpe + e];
-    chunks[i] = acc;
-  }
+  if (threadIdx.x == 0) trace_mark(a.status, 21);
   // exclusive scan of splits -> expert_base (E_virt <= 4 * blockDim)
   {
     const int per = (E_virt + blockDim.x - 1) / blockDim.x;
     const int lo = threadIdx.x * per;
     int local = 0;
     for (int q = 0; q < per; ++q)
-      if (lo + q < E_virt) local += a.splits[lo + q];
+      if (lo + q < E_virt) local += s_splits[lo + q];
     int total;
     int run = block_exclusive_scan(local, warp_tot, &total);
     for (int q = 0; q < per; ++q)
-      if (lo + q < E_virt) { a.expert_base[lo + q] = run; run += a.splits[lo + q]; }
-    if (threadIdx.x == 0) a.expert_base[E_virt] = total;
+      if (lo + q < E_virt) { a.expert_base[lo + q] = run; s_base[lo + q] = run; run += s_splits[lo + q]; }
+    if (threadIdx.x == 0) { a.expert_base[E_virt] = total; s_base[E_virt] = total; }
   }
   __syncthreads();
+  if (threadIdx.x == 0) trace_mark(a.status, 22);
   for (int e = threadIdx.x; e < E_virt; e += blockDim.x) {      // tile histograms -> tile bases, in place
-    int run = a.expert_base[e];
+    int run = s_base[e];
     for (int b = 0; b < n_blocks; ++b) {
       const int h = a.tile_hist[(size_t)b * E_virt + e];
       a.tile_hist[(size_t)b * E_virt + e] = run;
@@ -277,8 +293,9 @@ __device__ void meta_scan_body(MetaArgs& a, int* chunks) {
     }
   }
   if (threadIdx.x == 0) {
+    trace_mark(a.status, 23);
     long long out[8];
-    demands_from_chunks(chunks, a.uc, R, a.L, a.relay_slots, a.direct, a.caps, out);
+    demands_from_chunks(chunks, s_uc, R, a.L, a.relay_slots, a.direct, a.caps, out);
     for (int i = 0; i < 8; ++i) a.demands[i] = out[i];
     viol = out[7];
     if (a.status) {
@@ -287,17 +304,18 @@ __device__ void meta_scan_body(MetaArgs& a, int* chunks) {
     }
   }
   __syncthreads();
+  if (threadIdx.x == 0) trace_mark(a.status, 24);
   // ---- this rank's GEMM schedule: token tiles of its groups in row order, one thread per group;
   //      groups marked as moved-in (bit 30 of their schedule word) go last (their weights land late)
   if (a.n_tiles != nullptr) {
     const int g0 = a.my_rank * a.gpe;
-    const int m_start = a.expert_base[g0];
-    const int m_this = a.expert_base[g0 + a.gpe] - m_start;
+    const int m_start = s_base[g0];
+    const int m_this = s_base[g0 + a.gpe] - m_start;
     const bool run_ok = viol == 0 && m_this <= a.recv_cap;
     const int e = threadIdx.x;                   // gpe <= blockDim.x
     int me = 0, late = 0;
     if (e >= 1 && e < a.gpe && run_ok) {
-      me = a.splits[g0 + e];
+      me = s_splits[g0 + e];
       late = a.group_order != nullptr ? ((a.group_order[e] >> 30) & 1) : 0;
     }
     const int nt = (me + kTileRowsMax - 1) / kTileRowsMax;
@@ -305,7 +323,7 @@ __device__ void meta_scan_body(MetaArgs& a, int* chunks) {
     const int pre_early = block_exclusive_scan(late ? 0 : nt, warp_tot, &tot_early);
     const int pre_late = block_exclusive_scan(late ? nt : 0, warp_tot, &tot_late);
     const int first = late ? tot_early + pre_late : pre_early;
-    const int off = e < a.gpe ? a.expert_base[g0 + (e < a.gpe ? e : 0)] - m_start : 0;
+    const int off = e < a.gpe ? s_base[g0 + (e < a.gpe ? e : 0)] - m_start : 0;
     for (int t = 0; t < nt; ++t) {
       const int slot = first + t;
       if (slot < a.max_tiles) {
@@ -316,6 +334,7 @@ __device__ void meta_scan_body(MetaArgs& a, int* chunks) {
       }
     }
     if (threadIdx.x == 0) {
+      trace_mark(a.status, 25);
       a.m_this[0] = m_this;
       a.m_this[1] = m_start;
       *a.n_tiles = min(tot_early + tot_late, a.max_tiles);
@@ -330,20 +349,20 @@ __device__ void meta_scan_body(MetaArgs& a, int* chunks) {
     long long max_col = 0;
     for (int d = 0; d < W; ++d) {
       long long col = 0;
-      for (int s = 0; s < W; ++s) col += region_rows(a.uc, W, L, s, d);
+      for (int s = 0; s < W; ++s) col += region_rows(s_uc, W, L, s, d);
       if (col > max_col) max_col = col;
     }
     for (int s = 0; s < W; ++s) {
       for (int d = 0; d < W; ++d) {
         const long long cv = chunks[s * W + d];
-        const long long uv = a.uc[s * ucw + d];
+        const long long uv = s_uc[s * ucw + d];
         if (!(uv >= 0 && uv <= cv && ((uv > 0) == (cv > 0)))) err |= 4;
-        if (uv > a.uc[s * ucw + W + d / L]) err |= 8;
+        if (uv > s_uc[s * ucw + W + d / L]) err |= 8;
       }
       for (int n = 0; n < NN; ++n) {
         long long su = 0;
-        for (int l = 0; l < L; ++l) su += a.uc[s * ucw + n * L + l];
-        if (a.uc[s * ucw + W + n] > su) err |= 8;
+        for (int l = 0; l < L; ++l) su += s_uc[s * ucw + n * L + l];
+        if (s_uc[s * ucw + W + n] > su) err |= 8;
       }
     }
     long long* P = a.dplan;
@@ -353,9 +372,9 @@ __device__ void meta_scan_body(MetaArgs& a, int* chunks) {
     seg_tab[0] = 0;
     for (int n = 0; n < NN; ++n) {
       if (n == me_n) {
-        for (int dl = 0; dl < L; ++dl) { seg += a.uc[rank * ucw + n * L + dl]; seg_tab[++si] = seg; }
+        for (int dl = 0; dl < L; ++dl) { seg += s_uc[rank * ucw + n * L + dl]; seg_tab[++si] = seg; }
       } else {
-        seg += a.uc[rank * ucw + W + n];
+        seg += s_uc[rank * ucw + W + n];
         seg_tab[++si] = seg;
       }
     }
@@ -364,8 +383,8 @@ __device__ void meta_scan_body(MetaArgs& a, int* chunks) {
     for (int dl = 0; dl < L; ++dl) {
       const int d = me_n * L + dl;
       long long off = 0;
-      for (int s = 0; s < rank; ++s) off += region_rows(a.uc, W, L, s, d);
-      P[r0 + 3 * dl + 0] = a.uc[rank * ucw + d];
+      for (int s = 0; s < rank; ++s) off += region_rows(s_uc, W, L, s, d);
+      P[r0 + 3 * dl + 0] = s_uc[rank * ucw + d];
       P[r0 + 3 * dl + 1] = seg_tab[me_n + dl];
       P[r0 + 3 * dl + 2] = off;
     }
@@ -374,8 +393,8 @@ __device__ void meta_scan_body(MetaArgs& a, int* chunks) {
     long long m0 = 0;
     for (int s = 0; s < W; ++s) m0 += chunks[s * W + rank];
     long long off_me = 0;
-    for (int s = 0; s < rank; ++s) off_me += region_rows(a.uc, W, L, s, rank);
-    P[0] = m0; P[1] = seg_tab[nseg]; P[2] = a.uc[rank * ucw + rank]; P[3] = seg_tab[me_n + me_l]; P[4] = off_me;
+    for (int s = 0; s < rank; ++s) off_me += region_rows(s_uc, W, L, s, rank);
+    P[0] = m0; P[1] = seg_tab[nseg]; P[2] = s_uc[rank * ucw + rank]; P[3] = seg_tab[me_n + me_l]; P[4] = off_me;
     P[5] = err; P[6] = 0; P[7] = 0;
   }
   if (threadIdx.x == 64 && a.cplan != nullptr) {
@@ -413,6 +432,7 @@ __global__ void __launch_bounds__(kMetaThreads) meta_pass2_kernel(MetaArgs a) {
   const int* tbase = a.tile_hist + (size_t)blockIdx.x * E_virt;
   const int T = a.tokens_per_tile * a.K;
   const int n_warps = (T + 31) / 32;
+  if (blockIdx.x == 0 && threadIdx.x == 0) trace_mark(a.status, TR_PASS2);
   int* wc = sm;                           // [n_warps][E_virt] copies of expert e in warp w, then their base
   for (int i = threadIdx.x; i < n_warps * E_virt; i += blockDim.x) wc[i] = 0;
   __syncthreads();

@@ -77,7 +77,7 @@ __global__ void loads_publish_kernel(const int* __restrict__ topk_own, int n_ent
   __threadfence_system();
   __syncthreads();
   if (threadIdx.x < world && flags.ptr[threadIdx.x] != nullptr)
-    st_release_sys(reinterpret_cast<unsigned long long*>(flags.ptr[threadIdx.x]) + rank, epoch);
+    st_relaxed_sys(reinterpret_cast<unsigned long long*>(flags.ptr[threadIdx.x]) + rank, epoch);
   if (threadIdx.x == 0 && ctr != nullptr) *ctr = epoch;
 }
 
@@ -451,7 +451,7 @@ __global__ void route_finish_kernel(FinishArgs a) {
     if (prev == gridDim.x - 1) {
       __threadfence_system();
       for (int p = 0; p < a.world; ++p)
-        if (a.flags.ptr[p]) st_release_sys(reinterpret_cast<unsigned long long*>(a.flags.ptr[p]) + a.my_rank, epoch);
+        if (a.flags.ptr[p]) st_relaxed_sys(reinterpret_cast<unsigned long long*>(a.flags.ptr[p]) + a.my_rank, epoch);
     }
   }
 }
@@ -468,8 +468,7 @@ __global__ void route_finish_kernel(FinishArgs a) {
 struct SimpleRouteArgs {
   const int* topk_own;
   const float* probs_own;
-  const int* l2p;
-  const int* lcnts;
+  const int* slot_of;      // [G] the only physical slot of every expert (-1: none)
   int SK, G, R, my_rank, world, first;
   int* phys_own;
   int* send_row;
@@ -477,41 +476,105 @@ struct SimpleRouteArgs {
   unsigned long long* ctr;
   unsigned int* block_counter;
   unsigned long long* status;
+  // optional: publish this rank's x in the same launch (blocks route_blocks .. gridDim-1 copy it)
+  int route_blocks;
+  const uint4* x;
+  uint4* xsym_even;
+  uint4* xsym_odd;
+  size_t x_vec;
+  PeerTable x_flags;
 };
 
+__device__ __forceinline__ int single_replica_slot(const SimpleRouteArgs& a, const int* slots, int e) {
+  if (e < 0 || e >= a.G) {
+    if (a.status) atomicOr(a.status + ST_ERROR, (unsigned long long)ERR_BAD_INDEX);
+    return 0;
+  }
+  const int p = slots[e];
+  if (p < 0) {
+    if (a.status) atomicOr(a.status + ST_ERROR, (unsigned long long)ERR_ROUTE);
+    return 0;
+  }
+  return p;
+}
+
+// slot_of[e] = first valid l2p entry of expert e (the placement's only replica when c_max == 1)
+__global__ void slot_table_kernel(const int* l2p, const int* lcnts, int G, int R, int* slot_of) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= G) return;
+  const int cnt = min(lcnts[e], R);
+  int p0 = -1;
+  for (int j = 0; j < cnt && p0 < 0; ++j)
+    if (l2p[e * R + j] >= 0) p0 = l2p[e * R + j];
+  slot_of[e] = p0;
+}
+
 __global__ void __launch_bounds__(256) route_simple_publish_kernel(SimpleRouteArgs a) {
+  if (blockIdx.x == 0 && threadIdx.x == 0) trace_mark(a.status, TR_ROUTE);
   const unsigned long long epoch = step_epoch(a.ctr, a.first != 0);
-  const PeerTable& dst = (epoch & 1) ? a.dst_odd : a.dst;
-  const int* wbits = reinterpret_cast<const int*>(a.probs_own);
-  for (int n = blockIdx.x * blockDim.x + threadIdx.x; n < a.SK; n += gridDim.x * blockDim.x) {
-    const int e = a.topk_own[n];
-    int p0 = 0;
-    if (e >= 0 && e < a.G) {
-      const int cnt = min(a.lcnts[e], a.R);
-      int j = 0;
-      while (j < cnt && a.l2p[e * a.R + j] < 0) ++j;
-      if (j < cnt) p0 = a.l2p[e * a.R + j];
-      else if (a.status) atomicOr(a.status + ST_ERROR, (unsigned long long)ERR_ROUTE);
-    } else if (a.status) {
-      atomicOr(a.status + ST_ERROR, (unsigned long long)ERR_BAD_INDEX);
-    }
-    const int wb = wbits[n];
-    a.phys_own[n] = p0;
-    if (a.send_row) { a.send_row[n] = p0; a.send_row[a.SK + n] = wb; }
-    for (int p = 0; p < a.world; ++p) {
-      int* row = reinterpret_cast<int*>(dst.ptr[p]) + (size_t)a.my_rank * 2 * a.SK;
-      row[n] = p0;
-      row[a.SK + n] = wb;
+  extern __shared__ int slots[];             // [G] staged copy of the slot table (routing blocks)
+  if ((int)blockIdx.x < a.route_blocks) {
+    for (int g = threadIdx.x; g < a.G; g += blockDim.x) slots[g] = a.slot_of[g];
+    __syncthreads();
+  }
+  if ((int)blockIdx.x >= a.route_blocks) {
+    // x publication blocks
+    uint4* xsym = (epoch & 1) ? a.xsym_odd : a.xsym_even;
+    const size_t nb = gridDim.x - a.route_blocks;
+    for (size_t i = (size_t)(blockIdx.x - a.route_blocks) * blockDim.x + threadIdx.x; i < a.x_vec; i += nb * blockDim.x)
+      xsym[i] = a.x[i];
+  } else {
+    const PeerTable& dst = (epoch & 1) ? a.dst_odd : a.dst;
+    const int* wbits = reinterpret_cast<const int*>(a.probs_own);
+    const int SK = a.SK;
+    const size_t row_off = (size_t)a.my_rank * 2 * SK;
+    if ((SK & 3) == 0) {
+      // four entries per thread, 16-byte stores into every rank's gather table
+      for (int q = blockIdx.x * blockDim.x + threadIdx.x; q < SK / 4; q += a.route_blocks * blockDim.x) {
+        const int4 e4 = reinterpret_cast<const int4*>(a.topk_own)[q];
+        const int4 w4 = reinterpret_cast<const int4*>(wbits)[q];
+        int4 p4;
+        p4.x = single_replica_slot(a, slots, e4.x);
+        p4.y = single_replica_slot(a, slots, e4.y);
+        p4.z = single_replica_slot(a, slots, e4.z);
+        p4.w = single_replica_slot(a, slots, e4.w);
+        reinterpret_cast<int4*>(a.phys_own)[q] = p4;
+        if (a.send_row) {
+          reinterpret_cast<int4*>(a.send_row)[q] = p4;
+          reinterpret_cast<int4*>(a.send_row + SK)[q] = w4;
+        }
+        for (int p = 0; p < a.world; ++p) {
+          int* row = reinterpret_cast<int*>(dst.ptr[p]) + row_off;
+          reinterpret_cast<int4*>(row)[q] = p4;
+          reinterpret_cast<int4*>(row + SK)[q] = w4;
+        }
+      }
+    } else {
+      for (int n = blockIdx.x * blockDim.x + threadIdx.x; n < SK; n += a.route_blocks * blockDim.x) {
+        const int p0 = single_replica_slot(a, slots, a.topk_own[n]);
+        const int wb = wbits[n];
+        a.phys_own[n] = p0;
+        if (a.send_row) { a.send_row[n] = p0; a.send_row[SK + n] = wb; }
+        for (int p = 0; p < a.world; ++p) {
+          int* row = reinterpret_cast<int*>(dst.ptr[p]) + row_off;
+          row[n] = p0;
+          row[SK + n] = wb;
+        }
+      }
     }
   }
-  __threadfence_system();
+  // one fence per block (thread 0, after the block barrier) orders every thread's stores before the
+  // block's arrival; the last block to arrive publishes the epoch words
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence_system();
     const unsigned int prev = atomicInc(a.block_counter, gridDim.x - 1);
     if (prev == gridDim.x - 1) {
       __threadfence_system();
-      for (int p = 0; p < a.world; ++p)
-        st_release_sys(reinterpret_cast<unsigned long long*>(a.flags.ptr[p]) + a.my_rank, epoch);
+      for (int p = 0; p < a.world; ++p) {
+        st_relaxed_sys(reinterpret_cast<unsigned long long*>(a.flags.ptr[p]) + a.my_rank, epoch);
+        if (a.x != nullptr) st_relaxed_sys(reinterpret_cast<unsigned long long*>(a.x_flags.ptr[p]) + a.my_rank, epoch);
+      }
       if (a.first && a.ctr != nullptr) *a.ctr = epoch;
     }
   }

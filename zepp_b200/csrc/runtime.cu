@@ -209,7 +209,7 @@ struct zepp_layer {
   __nv_bfloat16* panel;              // [S*K, H]
   // local buffers
   __nv_bfloat16 *recv, *act, *staging;
-  int *topk_own, *phys_own, *send_row, *route_ws, *p2l, *l2p, *lcnts, *p2l_try, *l2p_try;
+  int *slot_of, *topk_own, *phys_own, *send_row, *route_ws, *p2l, *l2p, *lcnts, *p2l_try, *l2p_try;
   float* probs_own;
   long long* route_stats;
   int *vce, *splits, *scatter_index, *sps, *uc, *tile_hist, *tile_uc, *expert_base;
@@ -235,6 +235,8 @@ struct zepp_layer {
   unsigned long long* step_ctr = nullptr;     // device-resident step counter (epoch of the running step)
   int c_max = 1;                              // largest replica count of the resident placement
   bool use_graphs = true;
+  const void* fuse_x = nullptr;       // x of a whole-step call, published by the routing kernel
+  const void* x_fused = nullptr;
   cudaStream_t capture_stream = nullptr;
   struct StepGraph {
     const void *ids, *wts, *x, *y;
@@ -299,6 +301,7 @@ static int layer_alloc(zepp_layer* l) {
   LA(l->l2p, l->G * R);
   LA(l->l2p_try, l->G * R);
   LA(l->lcnts, l->G);
+  LA(l->slot_of, l->G);
   LA(l->vce, (size_t)R * l->SK);
   LA(l->probs_all, (size_t)R * l->SK);
   LA(l->scatter_index, (size_t)R * l->SK);
@@ -418,6 +421,8 @@ extern "C" int zepp_layer_set_placement(zepp_layer* l, const int32_t* p2l, const
   CU_OK(cudaMemcpyAsync(l->p2l, p2l, (size_t)l->W * l->nlp * 4, cudaMemcpyHostToDevice, st));
   CU_OK(cudaMemcpyAsync(l->l2p, l2p, (size_t)l->G * l->W * 4, cudaMemcpyHostToDevice, st));
   CU_OK(cudaMemcpyAsync(l->lcnts, lcnts, (size_t)l->G * 4, cudaMemcpyHostToDevice, st));
+  slot_table_kernel<<<(l->G + 127) / 128, 128, 0, st>>>(l->l2p, l->lcnts, l->G, l->W, l->slot_of);
+  CU_OK(cudaGetLastError());
   CU_OK(cudaStreamSynchronize(st));
   l->c_max = 1;
   for (int g = 0; g < l->G; ++g) l->c_max = lcnts[g] > l->c_max ? lcnts[g] : l->c_max;
@@ -467,7 +472,7 @@ static MetaArgs layer_meta_args(zepp_layer* l) {
 }
 
 static size_t meta_smem(int R, int NN, int E_virt) {
-  const size_t a = (size_t)(E_virt + R + NN), b = (size_t)R * R;     // pass1 counters / the scan's chunk table
+  const size_t a = (size_t)(E_virt + R + NN), b = meta_scan_smem_ints(R, NN, E_virt);   // pass1 counters / the scan
   return (a > b ? a : b) * sizeof(int);
 }
 static size_t pass2_smem(int tokens_per_tile, int K, int E_virt) {
@@ -508,7 +513,7 @@ extern "C" int zepp_layer_prepare_phase(zepp_layer* l, int phase, const int32_t*
     if (ids) { l->ids_in = ids; l->wts_in = wts; }
     if (l->c_max <= 1) {
       SimpleRouteArgs sa{};
-      sa.topk_own = l->ids_in; sa.probs_own = l->wts_in; sa.l2p = l->l2p; sa.lcnts = l->lcnts;
+      sa.topk_own = l->ids_in; sa.probs_own = l->wts_in; sa.slot_of = l->slot_of;
       sa.SK = l->SK; sa.G = l->G; sa.R = R; sa.my_rank = me; sa.world = R; sa.first = needs_loads(l) ? 0 : 1;
       sa.phys_own = l->phys_own; sa.send_row = l->send_row; sa.dst = l->xchg_dst[0]; sa.dst_odd = l->xchg_dst[1];
       sa.flags = l->routing_flag_dst; sa.ctr = l->step_ctr; sa.block_counter = l->counters + 0; sa.status = l->status;
@@ -523,7 +528,17 @@ extern "C" int zepp_layer_prepare_phase(zepp_layer* l, int phase, const int32_t*
         route_kernel<<<(l->G + 7) / 8, 256, 0, st>>>(ra);
         LAUNCH_OK();
       }
-      route_simple_publish_kernel<<<(l->SK + 1023) / 1024, 256, 0, st>>>(sa);
+      sa.route_blocks = (l->SK / 4 + 255) / 256 > 0 ? (l->SK / 4 + 255) / 256 : 1;
+      if ((l->SK & 3) != 0) sa.route_blocks = (l->SK + 255) / 256;
+      int grid = sa.route_blocks;
+      if (l->fuse_x != nullptr && R > 1) {
+        // the caller's x is already known (zepp_layer_step): publish it from extra blocks of this launch
+        sa.x = (const uint4*)l->fuse_x; sa.xsym_even = (uint4*)l->xsym[0]; sa.xsym_odd = (uint4*)l->xsym[1];
+        sa.x_vec = (size_t)l->S * l->H / 8; sa.x_flags = l->x_flag_dst;
+        grid += 64;
+        l->x_fused = l->fuse_x;
+      }
+      route_simple_publish_kernel<<<grid, 256, l->G * sizeof(int), st>>>(sa);
       LAUNCH_OK();
     } else {
       RouteArgs ra{};
@@ -641,6 +656,10 @@ extern "C" int zepp_layer_forward_phase(zepp_layer* l, int phase, const void* x,
   const bool direct = l->cfg.strategy == 1;
   if (phase == 0) {
     l->x_self = x;
+    if (l->x_fused == x && x != nullptr) {     // already published by the routing kernel of this step
+      l->x_fused = nullptr;
+      return 0;
+    }
     if (l->W > 1) {
       const size_t n_vec = (size_t)l->S * l->H / 8;
       publish_x_kernel<<<64, 256, 0, st>>>((const uint4*)x, (uint4*)l->xsym[0], (uint4*)l->xsym[1], n_vec, l->rt->rank,
@@ -666,7 +685,7 @@ extern "C" int zepp_layer_forward_phase(zepp_layer* l, int phase, const void* x,
     GemmArgs g = layer_gemm_args(l, false);
     if (direct) {
       g.staging = l->staging;
-    } else {
+    } else if (l->W > 1) {
       g.done_flags = l->done_ptrs;
     }
     if (launch_gemm<MODE_DOWN_COMBINE>(l, l->tm_w2, l->tm_act, g, st)) return 1;
@@ -679,7 +698,8 @@ extern "C" int zepp_layer_forward_phase(zepp_layer* l, int phase, const void* x,
   }
   if (phase == 3) {
     combine_reduce_kernel<<<l->rt->sm_count * 2, 256, 0, st>>>(l->panel, (__nv_bfloat16*)y, l->S, l->K, l->H,
-                                                            l->done_flags, l->W, l->step_ctr, l->rt->wait_ns, l->status);
+                                                            l->W > 1 ? l->done_flags : nullptr, l->W, l->step_ctr,
+                                                            l->rt->wait_ns, l->status);
     LAUNCH_OK();
     return 0;
   }
@@ -695,6 +715,8 @@ extern "C" int zepp_layer_forward(zepp_layer* l, const void* x, void* y, void* s
 // One whole step in launch order.  x is published right after the first planning kernel, long before
 // the dispatch GEMM of any rank needs it, so the GEMM's wait for x never stalls on rank skew.
 static int step_enqueue(zepp_layer* l, const int32_t* ids, const float* wts, const void* x, void* y, void* stream) {
+  l->fuse_x = (!needs_loads(l) && l->c_max <= 1) ? x : nullptr;
+  l->x_fused = nullptr;
   if (zepp_layer_prepare_phase(l, 0, ids, wts, stream)) return 1;
   if (needs_loads(l)) {
     if (zepp_layer_forward_phase(l, 0, x, y, stream)) return 1;
@@ -704,6 +726,7 @@ static int step_enqueue(zepp_layer* l, const int32_t* ids, const float* wts, con
     if (zepp_layer_forward_phase(l, 0, x, y, stream)) return 1;
   }
   if (zepp_layer_prepare_phase(l, 2, ids, wts, stream)) return 1;
+  l->fuse_x = nullptr;
   for (int ph = 1; ph < 4; ++ph)
     if (zepp_layer_forward_phase(l, ph, x, y, stream)) return 1;
   return 0;
@@ -770,8 +793,18 @@ extern "C" int zepp_layer_status(zepp_layer* l, void* stream, uint64_t out[8]) {
   cudaStream_t st = (cudaStream_t)stream;
   CU_OK(cudaSetDevice(l->rt->device));
   CU_OK(cudaStreamSynchronize(st));
-  CU_OK(cudaMemcpy(out, l->status, ST_WORDS * 8, cudaMemcpyDeviceToHost));
+  CU_OK(cudaMemcpy(out, l->status, 8 * 8, cudaMemcpyDeviceToHost));
   CU_OK(cudaMemset(l->status, 0, 4 * 8));
+  return 0;
+}
+
+extern "C" int zepp_layer_trace(zepp_layer* l, void* stream, uint64_t out[32]) {
+  CU_OK(cudaSetDevice(l->rt->device));
+  CU_OK(cudaStreamSynchronize((cudaStream_t)stream));
+  CU_OK(cudaMemcpy(out, l->status, ST_WORDS * 8, cudaMemcpyDeviceToHost));
+  CU_OK(cudaMemset(l->status + TR_GEMM1_END, 0, 8));
+  CU_OK(cudaMemset(l->status + TR_GEMM2_END, 0, 8));
+  CU_OK(cudaMemset(l->status + TR_REDUCE_END, 0, 8));
   return 0;
 }
 

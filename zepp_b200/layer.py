@@ -213,6 +213,16 @@ class EPMoE(torch.nn.Module):
             what = ", ".join(n for b, n in _ERR_NAMES.items() if st[0] & b)
             raise RuntimeError(f"zepp_b200 step failed: {what} (wait id {st[1]}, peer/item {st[2]}, epoch {st[3]})")
 
+    TRACE_NAMES = ("route", "pass1", "pass1_go", "pass2", "gemm1", "gemm1_x", "gemm1_end", "gemm2", "gemm2_end",
+                   "reduce", "reduce_go", "reduce_end", "scan", "scan_counts", "scan_bases", "scan_demands",
+                   "scan_sched", "scan_end")
+
+    def trace(self):
+        """Device timeline of the last step: microseconds of each stamp after the step's first kernel."""
+        t = self._h.trace()[8:8 + len(self.TRACE_NAMES)]
+        t0 = t[0]
+        return {n: (v - t0) / 1e3 if v else None for n, v in zip(self.TRACE_NAMES, t)}
+
     def tables(self, *names):
         """Planner products of the last prepare (device tensors): see runtime.TABLES."""
         return [self._h.table(n) for n in names]

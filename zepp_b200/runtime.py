@@ -136,6 +136,11 @@ class LayerHandle:
         check(lib().zepp_layer_status(self.h, self._stream(), out))
         return [int(v) for v in out]
 
+    def trace(self):
+        out = (ctypes.c_uint64 * 32)()
+        check(lib().zepp_layer_trace(self.h, self._stream(), out))
+        return [int(v) for v in out]
+
     def launches(self):
         v = ctypes.c_int64()
         check(lib().zepp_layer_gpu_launches(self.h, ctypes.byref(v)))
