@@ -72,6 +72,11 @@ def _run_local(shape, W, L, S, strategy, zipf=0.0, seed=0, steps=2, check_plan=T
                     assert np.array_equal(t["uc"].cpu().numpy().reshape(uc.shape), uc), (r, "uc")
                     gpe = cfg.groups_per_rank
                     assert int(t["m_this"][0]) == int(splits[r * gpe:(r + 1) * gpe].sum())
+                    words, head = op.dispatch_plan_head(sps, uc, W, L, gpe, r, S * cfg.shape.topk, layers[r].caps.dispatch_recv)
+                    assert l.tables("dplan")[0].cpu().tolist()[:head] == words[:head], (r, "dplan")
+                    if W == L:
+                        so, sr, do, lo = op.combine_tables(sps, W, gpe, r)
+                        assert l.tables("cplan")[0].cpu().tolist() == np.concatenate([so, sr, do, lo]).tolist(), (r, "cplan")
     finally:
         for l in layers:
             l.close()

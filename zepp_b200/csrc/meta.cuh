@@ -70,6 +70,7 @@ struct MetaArgs {
 };
 
 __device__ void meta_scan_body(MetaArgs& a, int* chunks);
+__device__ void plan_heads(MetaArgs& a, const int* chunks, const int* s_uc);
 
 __global__ void __launch_bounds__(kMetaThreads) meta_pass1_kernel(MetaArgs a) {
   extern __shared__ int sm[];
@@ -340,47 +341,63 @@ __device__ void meta_scan_body(MetaArgs& a, int* sm) {
       *a.n_tiles = min(tot_early + tot_late, a.max_tiles);
     }
   }
-  // ---- plan heads
-  if (threadIdx.x == 32 && a.dplan != nullptr) {
+  plan_heads(a, chunks, s_uc);
+}
+
+// Dispatch plan head and combine tables from the step's chunk table and unique counts.  Nothing
+// on the GEMMs' path reads them: the layer computes them on request (plan_heads_kernel), the
+// stand-alone metadata entry point inline.
+__device__ void plan_heads(MetaArgs& a, const int* chunks, const int* s_uc) {
+  const int R = a.R, NN = a.R / a.L, ucw = R + NN;
+  // one warp each, lanes over destinations
+  __shared__ long long seg_tab[132];
+  const int lane_w = threadIdx.x & 31;
+  if ((threadIdx.x >> 5) == 1 && a.dplan != nullptr) {
     // header + send segments + round-0 triples (python/zepp/routing.py:510-554, 613-623)
     const int W = R, L = a.L, rank = a.my_rank, me_n = rank / L, me_l = rank % L;
     const int nseg = L + NN - 1;
-    long long err = 0;
-    long long max_col = 0;
-    for (int d = 0; d < W; ++d) {
+    long long err = 0, max_col = 0;
+    for (int d = lane_w; d < W; d += 32) {
       long long col = 0;
       for (int s = 0; s < W; ++s) col += region_rows(s_uc, W, L, s, d);
       if (col > max_col) max_col = col;
     }
-    for (int s = 0; s < W; ++s) {
-      for (int d = 0; d < W; ++d) {
-        const long long cv = chunks[s * W + d];
-        const long long uv = s_uc[s * ucw + d];
-        if (!(uv >= 0 && uv <= cv && ((uv > 0) == (cv > 0)))) err |= 4;
-        if (uv > s_uc[s * ucw + W + d / L]) err |= 8;
-      }
+    for (int i = lane_w; i < W * W; i += 32) {
+      const int s = i / W, d = i - s * W;
+      const long long cv = chunks[i];
+      const long long uv = s_uc[s * ucw + d];
+      if (!(uv >= 0 && uv <= cv && ((uv > 0) == (cv > 0)))) err |= 4;
+      if (uv > s_uc[s * ucw + W + d / L]) err |= 8;
+    }
+    for (int i = lane_w; i < W * NN; i += 32) {
+      const int s = i / NN, n = i - s * NN;
+      long long su = 0;
+      for (int l = 0; l < L; ++l) su += s_uc[s * ucw + n * L + l];
+      if (s_uc[s * ucw + W + n] > su) err |= 8;
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      err |= __shfl_xor_sync(0xffffffffu, err, o);
+      const long long m2 = __shfl_xor_sync(0xffffffffu, max_col, o);
+      if (m2 > max_col) max_col = m2;
+    }
+    if (lane_w == 0) {
+      long long seg = 0;
+      int si = 0;
+      seg_tab[0] = 0;
       for (int n = 0; n < NN; ++n) {
-        long long su = 0;
-        for (int l = 0; l < L; ++l) su += s_uc[s * ucw + n * L + l];
-        if (s_uc[s * ucw + W + n] > su) err |= 8;
+        if (n == me_n) {
+          for (int dl = 0; dl < L; ++dl) { seg += s_uc[rank * ucw + n * L + dl]; seg_tab[++si] = seg; }
+        } else {
+          seg += s_uc[rank * ucw + W + n];
+          seg_tab[++si] = seg;
+        }
       }
     }
+    __syncwarp();
     long long* P = a.dplan;
-    long long seg = 0;
-    int si = 0;
-    long long seg_tab[130];
-    seg_tab[0] = 0;
-    for (int n = 0; n < NN; ++n) {
-      if (n == me_n) {
-        for (int dl = 0; dl < L; ++dl) { seg += s_uc[rank * ucw + n * L + dl]; seg_tab[++si] = seg; }
-      } else {
-        seg += s_uc[rank * ucw + W + n];
-        seg_tab[++si] = seg;
-      }
-    }
-    for (int i = 0; i <= nseg; ++i) P[8 + i] = seg_tab[i];
+    for (int i = lane_w; i <= nseg; i += 32) P[8 + i] = seg_tab[i];
     const int r0 = 8 + nseg + 1;
-    for (int dl = 0; dl < L; ++dl) {
+    for (int dl = lane_w; dl < L; dl += 32) {
       const int d = me_n * L + dl;
       long long off = 0;
       for (int s = 0; s < rank; ++s) off += region_rows(s_uc, W, L, s, d);
@@ -388,40 +405,57 @@ __device__ void meta_scan_body(MetaArgs& a, int* sm) {
       P[r0 + 3 * dl + 1] = seg_tab[me_n + dl];
       P[r0 + 3 * dl + 2] = off;
     }
-    if (max_col > a.caps[1]) err |= 16;
-    if (seg_tab[nseg] > a.copies_per_rank) err |= 32;
-    long long m0 = 0;
-    for (int s = 0; s < W; ++s) m0 += chunks[s * W + rank];
-    long long off_me = 0;
-    for (int s = 0; s < rank; ++s) off_me += region_rows(s_uc, W, L, s, rank);
-    P[0] = m0; P[1] = seg_tab[nseg]; P[2] = s_uc[rank * ucw + rank]; P[3] = seg_tab[me_n + me_l]; P[4] = off_me;
-    P[5] = err; P[6] = 0; P[7] = 0;
+    if (lane_w == 0) {
+      if (max_col > a.caps[1]) err |= 16;
+      if (seg_tab[nseg] > a.copies_per_rank) err |= 32;
+      long long m0 = 0, off_me = 0;
+      for (int s = 0; s < W; ++s) m0 += chunks[s * W + rank];
+      for (int s = 0; s < rank; ++s) off_me += region_rows(s_uc, W, L, s, rank);
+      P[0] = m0; P[1] = seg_tab[nseg]; P[2] = s_uc[rank * ucw + rank]; P[3] = seg_tab[me_n + me_l]; P[4] = off_me;
+      P[5] = err; P[6] = 0; P[7] = 0;
+    }
   }
-  if (threadIdx.x == 64 && a.cplan != nullptr) {
+  if ((threadIdx.x >> 5) == 2 && a.cplan != nullptr) {
     // combine tables on one node (python/zepp/routing.py:656-669): C[s][d] rows owner s returns to home d
     const int W = R, rank = a.my_rank;
     long long* so = a.cplan;
     long long* sr = so + W + 1;
     long long* dof = sr + W;
     long long* lo = dof + W;
-    long long acc = 0;
-    so[0] = 0;
-    for (int d = 0; d < W; ++d) {
-      const long long c = chunks[d * W + rank];
-      sr[d] = c;
-      acc += c;
-      so[d + 1] = acc;
+    for (int d = lane_w; d < W; d += 32) {
+      sr[d] = chunks[d * W + rank];
       long long before = 0;
       for (int s = 0; s < rank; ++s) before += chunks[d * W + s];
       dof[d] = before;
     }
-    acc = 0;
-    lo[0] = 0;
-    for (int s = 0; s < W; ++s) {
-      acc += chunks[rank * W + s];
-      lo[s + 1] = acc;
+    if (lane_w == 0) {
+      long long acc = 0;
+      so[0] = 0;
+      for (int d = 0; d < W; ++d) { acc += chunks[d * W + rank]; so[d + 1] = acc; }
+    }
+    if (lane_w == 1) {
+      long long acc = 0;
+      lo[0] = 0;
+      for (int s = 0; s < W; ++s) { acc += chunks[rank * W + s]; lo[s + 1] = acc; }
     }
   }
+}
+
+// sps / uc of the last step -> plan heads (one block; run on request, off the step's path)
+__global__ void __launch_bounds__(128) plan_heads_kernel(MetaArgs a) {
+  extern __shared__ int sm[];
+  const int R = a.R, NN = a.R / a.L, E_virt = a.R * a.gpe, ucw = R + NN;
+  int* chunks = sm;
+  int* s_uc = sm + R * R;
+  for (int i = threadIdx.x; i < R * R; i += blockDim.x) {
+    const int s = i / R, d = i - s * R;
+    int acc = 0;
+    for (int e = 0; e < a.gpe; ++e) acc += a.sps[s * E_virt + d * a.gpe + e];
+    chunks[i] = acc;
+  }
+  for (int i = threadIdx.x; i < R * ucw; i += blockDim.x) s_uc[i] = a.uc[i];
+  __syncthreads();
+  plan_heads(a, chunks, s_uc);
 }
 
 __global__ void __launch_bounds__(kMetaThreads) meta_pass2_kernel(MetaArgs a) {

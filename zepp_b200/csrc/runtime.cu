@@ -459,7 +459,7 @@ static MetaArgs layer_meta_args(zepp_layer* l) {
   m.sps = l->sps; m.uc = l->uc; m.demands = l->demands;
   for (int i = 0; i < 8; ++i) m.caps[i] = l->cfg.caps[i];
   m.direct = l->cfg.strategy == 1; m.relay_slots = 2;
-  m.dplan = l->dplan; m.cplan = l->NN == 1 ? l->cplan : nullptr; m.copies_per_rank = l->SK;
+  m.dplan = nullptr; m.cplan = nullptr; m.copies_per_rank = l->SK;     // plan heads: on request (zepp_layer_table)
   m.tile_hist = l->tile_hist; m.tile_uc = l->tile_uc; m.expert_base = l->expert_base;
   m.n_tiles = l->n_tiles; m.tile_group = l->tile_group; m.tile_row0 = l->tile_row0; m.tile_rows = l->tile_rows;
   m.tile_ready = l->tile_ready; m.max_tiles = l->max_tiles; m.recv_cap = l->cap; m.m_this = l->m_this;
@@ -826,8 +826,20 @@ extern "C" int zepp_layer_table(zepp_layer* l, int which, void** p, size_t* byte
     case ZEPP_T_SPS: *p = l->sps; *bytes = R * l->E_virt * 4; break;
     case ZEPP_T_UC: *p = l->uc; *bytes = R * (R + l->NN) * 4; break;
     case ZEPP_T_DEMANDS: *p = l->demands; *bytes = 64; break;
-    case ZEPP_T_DPLAN: *p = l->dplan; *bytes = (size_t)zepp_dispatch_plan_words(l->L, l->NN) * 8; break;
-    case ZEPP_T_CPLAN: *p = l->cplan; *bytes = (4 * R + 2) * 8; break;
+    case ZEPP_T_DPLAN:
+    case ZEPP_T_CPLAN: {
+      // computed on request from the last step's counts; synchronises the device
+      CU_OK(cudaSetDevice(l->rt->device));
+      CU_OK(cudaDeviceSynchronize());
+      MetaArgs m = layer_meta_args(l);
+      m.dplan = l->dplan;
+      m.cplan = l->NN == 1 ? l->cplan : nullptr;
+      plan_heads_kernel<<<1, 128, (size_t)(l->W * l->W + l->W * (l->W + l->NN)) * sizeof(int), 0>>>(m);
+      CU_OK(cudaGetLastError());
+      CU_OK(cudaDeviceSynchronize());
+      if (which == ZEPP_T_CPLAN) { *p = l->cplan; *bytes = (4 * R + 2) * 8; break; }
+      *p = l->dplan; *bytes = (size_t)zepp_dispatch_plan_words(l->L, l->NN) * 8; break;
+    }
     case ZEPP_T_ROUTE_WS: *p = l->route_ws; *bytes = (size_t)zepp_route_workspace_ints(l->G, l->W) * 4; break;
     case ZEPP_T_SWAP_BLOCK: *p = l->swap_block; *bytes = (size_t)zepp_swap_decide_out_ints(l->W, l->G, l->nlp, 8) * 8; break;
     case ZEPP_T_M_THIS: *p = l->m_this; *bytes = 8; break;
