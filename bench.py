@@ -233,9 +233,12 @@ def main():
     sampler.start()
     t_begin, t_end = ev(), ev()
     t_begin.record()
+    h0 = time.perf_counter()
     for i in range(args.steps):
         step_resident(i)
+    host_us = (time.perf_counter() - h0) / args.steps * 1e6      # host enqueue time per step (no sync inside)
     t_end.record()
+    steady = layer.trace()           # device stamps of the last step of the timed loop (steady state)
     barrier()
     launches = layer.gpu_launches - launches0
     layer.check()
@@ -270,6 +273,13 @@ def main():
     ms_e2e = max_over_ranks(t0.elapsed_time(t1)) / args.steps
     layer.check()
 
+    if world > 1:
+        steady_all = [None] * world
+        dist.all_gather_object(steady_all, {k: steady[k] for k in ("pass1", "pass1_go", "pass2", "gemm1", "gemm1_x",
+                                                                   "gemm1_end", "gemm2", "gemm2_end", "reduce", "reduce_go",
+                                                                   "reduce_end", "gather_end", "first_items")} | {"host_us": host_us})
+    else:
+        steady_all = [steady]
     # ---- roofline of the dispatch GEMM kernel (HBM bound at these row counts)
     H, I, K = shape.hidden, shape.ffn_hidden, shape.topk
     splits, m_this = layer.tables("splits", "m_this")
@@ -296,6 +306,8 @@ def main():
                    "timed": "prepare (device planning) + forward"},
         "latency_us": ms_step * 1e3,
         "device_timeline_us": timeline,
+        "host_enqueue_us_per_step": host_us,
+        "steady_timeline_us": steady_all,
         "breakdown_us": {"plan": plan_ms * 1e3, "dispatch_gemm": gemm1_ms * 1e3, "combine_gemm_reduce": comb_ms * 1e3},
         "roofline_layer": {"t_flop_us": t_flop * 1e6, "t_hbm_weights_us": t_hbm * 1e6,
                            "frac_of_3term": max(t_flop, t_hbm) / (ms_step * 1e-3), "rows_this_rank": m_r},

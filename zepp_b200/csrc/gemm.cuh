@@ -31,6 +31,7 @@ constexpr int kTileK = 64;        // bf16 elements per smem row = 128 bytes = on
 constexpr int kWTileBytes = kTileM * kTileK * 2;   // 16 KB
 constexpr int kXTileBytes = kTileN * kTileK * 2;   // 16 KB
 constexpr int kAccStages = 2;
+constexpr int kMaxGatherWarps = 8;     // warps 6.. of a dispatch GEMM CTA in fused mode (4 or 8, chosen at launch)
 constexpr int kMaxTilesSmem = 1024;   // token tiles of one rank and step held in shared memory
 
 enum GemmMode : int { MODE_GATE_UP_SWIGLU = 0, MODE_SINGLE_GELU = 1, MODE_DOWN_COMBINE = 2 };
@@ -105,7 +106,7 @@ __device__ __forceinline__ __nv_bfloat16 gelu_bf16(float acc) {
 }
 
 template <int MODE>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(192 + 32 * kMaxGatherWarps, 1)
 moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x32,
                 const __grid_constant__ CUtensorMap tm_x64, const __grid_constant__ CUtensorMap tm_x128,
                 const GemmArgs a) {
@@ -123,6 +124,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
   __shared__ int s_row0[kMaxTilesSmem], s_gr[kMaxTilesSmem];      // first row; (group << 9) | rows
   __shared__ __align__(16) __nv_bfloat16 s_stage[2][32][kTileM];   // epilogue transpose buffers
   __shared__ int s_epi_ok;
+  __shared__ int s_pref[kMaxTilesSmem + 1];                        // rows before tile i in schedule order
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -143,6 +145,22 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     s_gr[i] = (a.tt.tile_group[i] << 9) | (a.tt.tile_rows[i] & 0x1FF);
   }
 
+  if (MODE != MODE_DOWN_COMBINE && a.gather && warp == 2) {
+    // exclusive prefix of the tiles' row counts (read straight from the global table: the shared
+    // copy above is filled by other threads and only ordered by the barrier below)
+    int carry = 0;
+    for (int i0 = 0; i0 < n_tiles; i0 += 32) {
+      const int v = i0 + lane < n_tiles ? a.tt.tile_rows[i0 + lane] : 0;
+      int incl = v;
+      for (int off = 1; off < 32; off <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += u;
+      }
+      if (i0 + lane < n_tiles) s_pref[i0 + lane] = carry + incl - v;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) s_pref[n_tiles] = carry;
+  }
   if (threadIdx.x == 0) {
     if (blockIdx.x == 0) trace_mark(a.status, MODE == MODE_DOWN_COMBINE ? TR_GEMM2 : TR_GEMM1);
     abort_flag = 0;
@@ -187,22 +205,53 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         const uint32_t x_bytes = (rows <= 32 ? 32u : (rows <= 64 ? 64u : 128u)) * (kTileK * 2);
         const uint32_t tx = (Cfg::kDual ? 2u : 1u) * kWTileBytes + x_bytes;
         const int w_row = grp * a.w_rows_per_group + j * kTileM;
+        int kb_first = 0;
         if (MODE != MODE_DOWN_COMBINE && a.gather) {
-          // rows of this tile are pulled by gather warps (of any CTA): wait until all have landed
-          const unsigned long long t0 = globaltimer_ns();
-          bool ok = true;
-          while (ld_acquire_gpu_u32(a.tile_ready + ti) < (unsigned int)rows) {
-            if (*abortp || globaltimer_ns() - t0 > a.flag_limit_ns) { ok = false; break; }
-            __nanosleep(64);
+          // rows of this tile are pulled by gather warps (of any CTA).  If they have not all landed yet,
+          // start streaming the weight tiles of the first stages, then wait, then add the token tiles
+          if (ld_acquire_gpu_u32(a.tile_ready + ti) < (unsigned int)rows) {
+            const int pre = k_blocks < STAGES ? k_blocks : STAGES;
+            const int stage0 = stage;
+            bool ok = true;
+            for (int kb = 0; kb < pre && ok; ++kb) {
+              if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abortp, a.mbar_limit)) {
+                record_timeout(a.status, WAIT_MBAR_EMPTY, item, kb);
+                ok = false;
+                break;
+              }
+              uint8_t* st = smem + stage * Cfg::kStageBytes;
+              mbar_expect_tx(&full_bar[stage], tx);
+              tma_load_2d(st, &tm_w, &full_bar[stage], kb * kTileK, w_row);
+              if (Cfg::kDual) tma_load_2d(st + kWTileBytes, &tm_w, &full_bar[stage], kb * kTileK, w_row + a.up_row_offset);
+              if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+            const unsigned long long t0 = globaltimer_ns();
+            while (ok && ld_acquire_gpu_u32(a.tile_ready + ti) < (unsigned int)rows) {
+              if (*abortp || globaltimer_ns() - t0 > a.flag_limit_ns) {
+                record_timeout(a.status, WAIT_TILE_READY, ti, (long long)epoch);
+                ok = false;
+                break;
+              }
+              __nanosleep(64);
+            }
+            if (!ok) {
+              abort_flag = 1;
+              break;
+            }
+            fence_proxy_async();      // generic-proxy writes of the gather -> async-proxy TMA reads
+            int sx = stage0;
+            for (int kb = 0; kb < pre; ++kb) {
+              tma_load_2d(smem + sx * Cfg::kStageBytes + (Cfg::kDual ? 2 : 1) * kWTileBytes, tmx, &full_bar[sx],
+                          kb * kTileK, row0);
+              if (++sx == STAGES) sx = 0;
+            }
+            kb_first = pre;
+          } else {
+            fence_proxy_async();
           }
-          if (!ok) {
-            record_timeout(a.status, WAIT_TILE_READY, ti, (long long)epoch);
-            abort_flag = 1;
-            break;
-          }
-          fence_proxy_async();      // generic-proxy writes of the gather -> async-proxy TMA reads
+          if (item == item_first) trace_mark_max(a.status, 31);     // latest first-item start over the CTAs
         }
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = kb_first; kb < k_blocks; ++kb) {
           if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abortp, a.mbar_limit)) {
             record_timeout(a.status, WAIT_MBAR_EMPTY, item, kb);
             abort_flag = 1;
@@ -353,7 +402,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
   } else {
     // ------------------------------------------------------------------ gather warps (fused dispatch)
     if (MODE != MODE_DOWN_COMBINE && a.gather) {
-      const int gw = warp - 6;                  // 0..3
+      const int gw = warp - 6;                  // 0..gather warps-1
       // every source must have published its x for this step
       bool ok = true;
       if (a.x_flags != nullptr && lane < a.world) {
@@ -367,48 +416,88 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
       if (!ok) {
         if (lane == 0) abort_flag = 1;
       } else {
-        // rows are pulled in schedule order (tile by tile, the order the GEMM consumes them); row q of
-        // the step goes to gather warp (q mod all gather warps), so every SM keeps loads in flight
+        // Rows are pulled in schedule order: row q of the step belongs to gather warp (q mod all
+        // gather warps), so every SM keeps loads in flight.  A warp first lists up to 32 of its rows
+        // (lane j keeps the j-th), fetches their source tokens in one round trip, then streams the
+        // rows two at a time.
         const int vec_per_row = a.k_extent / 8;                 // 16-byte vectors per row
-        const int n_warps = gridDim.x * 4;
-        const int my_warp = blockIdx.x * 4 + gw;
-        int base = 0;
-        for (int ti = 0; ti < n_tiles; ++ti) {
-          const int row0 = s_row0[ti];
-          const int rows = s_gr[ti] & 0x1FF;
-          int first = (my_warp - base) % n_warps;
-          if (first < 0) first += n_warps;
-          base += rows;
-          for (int r = first; r < rows; r += n_warps) {
-            const int tok = a.row_tok[row0 + r];
-            const int src = tok / a.tokens_per_rank;
-            const int t = tok - src * a.tokens_per_rank;
-            if (tok >= 0 && src < a.world) {
-              const __nv_bfloat16* xb = (src == a.rank && a.x_self != nullptr)
-                                            ? a.x_self : ((epoch & 1) ? a.x_ptrs_odd[src] : a.x_ptrs[src]);
-              const uint4* sp = reinterpret_cast<const uint4*>(xb + (size_t)t * a.k_extent);
-              uint4* dp = reinterpret_cast<uint4*>(a.recv + (size_t)(row0 + r) * a.k_extent);
-              for (int v0 = 0; v0 < vec_per_row; v0 += 32 * 8) {
-                uint4 buf[8];
-#pragma unroll
-                for (int q = 0; q < 8; ++q) {
-                  const int v = v0 + q * 32 + lane;
-                  if (v < vec_per_row) buf[q] = sp[v];
+        const int gather_warps = (int)(blockDim.x >> 5) - 6;
+        const int n_warps = gridDim.x * gather_warps;
+        const int my_warp = blockIdx.x * gather_warps + gw;
+        const int total_rows = s_pref[n_tiles];
+        for (int g0 = my_warp; g0 < total_rows; g0 += 32 * n_warps) {
+          {
+            {
+              // lane j takes this warp's j-th row of the list: a binary search of the prefix table
+              const int g = g0 + lane * n_warps;
+              int my_r = -1, my_ti = 0;
+              if (g < total_rows) {
+                int lo = 0, hi = n_tiles - 1;
+                while (lo < hi) {
+                  const int mid = (lo + hi + 1) >> 1;
+                  if (s_pref[mid] <= g) lo = mid; else hi = mid - 1;
                 }
-#pragma unroll
-                for (int q = 0; q < 8; ++q) {
-                  const int v = v0 + q * 32 + lane;
-                  if (v < vec_per_row) dp[v] = buf[q];
-                }
+                my_ti = lo;
+                my_r = s_row0[lo] + (g - s_pref[lo]);
               }
-            } else if (lane == 0 && a.status != nullptr) {
-              atomicOr(a.status + ST_ERROR, (unsigned long long)ERR_BAD_INDEX);
+              const int cnt = __popc(__ballot_sync(0xffffffffu, g < total_rows));
+              const int n = cnt;
+              const int tok = lane < n ? a.row_tok[my_r] : -1;
+              // two rows at a time (16 x 512 bytes of loads in flight per warp); a fence and the tile
+              // credits after every pair, so early tiles are complete early
+              for (int j0 = 0; j0 < n; j0 += 2) {
+                const int j1 = j0 + 2 < n ? j0 + 2 : n;
+                for (int j = j0; j < j1; j += 2) {
+                  const uint4* srcA = nullptr;
+                  const uint4* srcB = nullptr;
+                  uint4* dstA = nullptr;
+                  uint4* dstB = nullptr;
+#pragma unroll
+                  for (int h = 0; h < 2; ++h) {
+                    const int rr = __shfl_sync(0xffffffffu, my_r, (j + h) & 31);
+                    const int tk = __shfl_sync(0xffffffffu, tok, (j + h) & 31);
+                    if (j + h < j1) {
+                      const int src = tk >= 0 ? tk / a.tokens_per_rank : -1;
+                      if (src >= 0 && src < a.world) {
+                        const int t = tk - src * a.tokens_per_rank;
+                        const __nv_bfloat16* xb = (src == a.rank && a.x_self != nullptr)
+                                                      ? a.x_self : ((epoch & 1) ? a.x_ptrs_odd[src] : a.x_ptrs[src]);
+                        const uint4* sp = reinterpret_cast<const uint4*>(xb + (size_t)t * a.k_extent);
+                        uint4* dp = reinterpret_cast<uint4*>(a.recv + (size_t)rr * a.k_extent);
+                        if (h == 0) { srcA = sp; dstA = dp; } else { srcB = sp; dstB = dp; }
+                      } else if (lane == 0 && a.status != nullptr) {
+                        atomicOr(a.status + ST_ERROR, (unsigned long long)ERR_BAD_INDEX);
+                      }
+                    }
+                  }
+                  for (int v0 = 0; v0 < vec_per_row; v0 += 256) {
+                    uint4 ba[8], bb[8];
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                      const int v = v0 + q * 32 + lane;
+                      if (v < vec_per_row) {
+                        if (srcA != nullptr) ba[q] = srcA[v];
+                        if (srcB != nullptr) bb[q] = srcB[v];
+                      }
+                    }
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                      const int v = v0 + q * 32 + lane;
+                      if (v < vec_per_row) {
+                        if (dstA != nullptr) dstA[v] = ba[q];
+                        if (dstB != nullptr) dstB[v] = bb[q];
+                      }
+                    }
+                  }
+                }
+                __threadfence();
+                __syncwarp();
+                if (lane >= j0 && lane < j1) atomicAdd(a.tile_ready + my_ti, 1u);
+              }
             }
-            __threadfence();
-            __syncwarp();
-            if (lane == 0) atomicAdd(a.tile_ready + ti, 1u);
           }
         }
+        if (lane == 0) trace_mark_max(a.status, 30);                 // gather finished (latest warp)
       }
     }
   }

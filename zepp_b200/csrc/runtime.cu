@@ -622,7 +622,8 @@ static GemmArgs layer_gemm_args(zepp_layer* l, bool first) {
 
 template <int MODE>
 static int launch_gemm(zepp_layer* l, const CUtensorMap& tw, const CUtensorMap* tx, GemmArgs& g, cudaStream_t st) {
-  const int threads = g.gather ? 320 : 192;
+  // more gather warps when most rows cross NVLink (latency-bound pulls), fewer when they are local
+  const int threads = g.gather ? 192 + 32 * (l->W >= 4 ? kMaxGatherWarps : 4) : 192;
   const int grid = l->rt->sm_count;
   const size_t smem = GemmCfg<MODE>::kSmemBytes;
   if (g.gather) {
@@ -805,6 +806,7 @@ extern "C" int zepp_layer_trace(zepp_layer* l, void* stream, uint64_t out[32]) {
   CU_OK(cudaMemset(l->status + TR_GEMM1_END, 0, 8));
   CU_OK(cudaMemset(l->status + TR_GEMM2_END, 0, 8));
   CU_OK(cudaMemset(l->status + TR_REDUCE_END, 0, 8));
+  CU_OK(cudaMemset(l->status + 30, 0, 16));
   return 0;
 }
 

@@ -215,7 +215,7 @@ class EPMoE(torch.nn.Module):
 
     TRACE_NAMES = ("route", "pass1", "pass1_go", "pass2", "gemm1", "gemm1_x", "gemm1_end", "gemm2", "gemm2_end",
                    "reduce", "reduce_go", "reduce_end", "scan", "scan_counts", "scan_bases", "scan_demands",
-                   "scan_sched", "scan_end", "dplan_end", "cplan_end", "dplan_start", "dplan_mid")
+                   "scan_sched", "scan_end", "dplan_end", "cplan_end", "dplan_start", "dplan_mid", "gather_end", "first_items")
 
     def trace(self):
         """Device timeline of the last step: microseconds of each stamp after the step's first kernel."""
