@@ -229,8 +229,8 @@ def main():
     sampler = ClockSampler(local_rank)
     names = ("start", "plan_comm", "place", "plan", "dispatch", "act", "combine")
     launches0 = layer.gpu_launches
+    sampler.start()                  # before the barrier: NVML start-up time differs per rank
     barrier()
-    sampler.start()
     t_begin, t_end = ev(), ev()
     t_begin.record()
     h0 = time.perf_counter()
@@ -239,6 +239,7 @@ def main():
     host_us = (time.perf_counter() - h0) / args.steps * 1e6      # host enqueue time per step (no sync inside)
     t_end.record()
     steady = layer.trace()           # device stamps of the last step of the timed loop (steady state)
+    ring = layer.step_ring()
     barrier()
     launches = layer.gpu_launches - launches0
     layer.check()
@@ -307,6 +308,7 @@ def main():
         "latency_us": ms_step * 1e3,
         "device_timeline_us": timeline,
         "host_enqueue_us_per_step": host_us,
+        "last_steps_start_end_us": ring,
         "steady_timeline_us": steady_all,
         "breakdown_us": {"plan": plan_ms * 1e3, "dispatch_gemm": gemm1_ms * 1e3, "combine_gemm_reduce": comb_ms * 1e3},
         "roofline_layer": {"t_flop_us": t_flop * 1e6, "t_hbm_weights_us": t_hbm * 1e6,

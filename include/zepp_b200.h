@@ -90,10 +90,10 @@ enum {
   ZEPP_T_GATE = 21, ZEPP_T_SCHED = 22
 };
 /* Device timeline of the last step (no counterpart in the reference, whose brackets are host-recorded events,
- * bench/replay.py:134-167): synchronises `stream` and copies 32 words; words 8..19 are globaltimer ns stamps:
+ * bench/replay.py:134-167): synchronises `stream` and copies 64 words (32..47 / 48..63: start / end stamps of the last 16 steps); words 8..19 are globaltimer ns stamps:
  * route, pass1, pass1 after its wait, pass2, dispatch GEMM start / x ready / end, combine GEMM start / end,
  * reduce start / after its wait / end. */
-int zepp_layer_trace(zepp_layer* layer, void* stream, uint64_t out[32]);
+int zepp_layer_trace(zepp_layer* layer, void* stream, uint64_t out[64]);
 int zepp_layer_gpu_launches(zepp_layer* layer, int64_t* out);  /* kernels launched so far by this layer */
 
 /* ---- stand-alone planner entry points (one GPU plays every rank: they take R, L, my_rank) ------ */

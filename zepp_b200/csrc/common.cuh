@@ -22,7 +22,8 @@ enum StatusWord : int {
   // device timeline of the last step (globaltimer ns), written by block 0 / the last block of each kernel
   TR_ROUTE = 8, TR_PASS1 = 9, TR_PASS1_GO = 10, TR_PASS2 = 11, TR_GEMM1 = 12, TR_GEMM1_X = 13, TR_GEMM1_END = 14,
   TR_GEMM2 = 15, TR_GEMM2_END = 16, TR_REDUCE = 17, TR_REDUCE_GO = 18, TR_REDUCE_END = 19,
-  ST_WORDS = 32
+  TR_RING = 32,        // start stamps of the last 16 steps (slot = epoch % 16), then their end stamps
+  ST_WORDS = 64
 };
 enum ErrorBit : unsigned long long {
   ERR_TIMEOUT = 1ull,        // a bounded wait ran out

@@ -28,6 +28,87 @@ __global__ void publish_x_kernel(const uint4* __restrict__ x, uint4* __restrict_
   }
 }
 
+// Staged dispatch push (overlap strategy, more than one rank).  As soon as a rank knows the owners
+// of its own copies -- before the routing exchange -- it stores every token row once into the
+// staging region stage[me] of each rank that owns at least one of the token's copies, at slot =
+// number of earlier tokens of this rank that also go to that rank (the reference's pack-push dedup,
+// src/dwire/dispatch_wire.cu:107-210 with the unique counts of python/zepp/routing.py:326-328).
+// The NVLink transfer runs while the planning kernels run; the receiver derives the same slots from
+// the gathered routing and its dispatch GEMM gathers from local memory.  Posted stores, no loads
+// across NVLink.  A block owns a range of tokens; it recounts the slots of the tokens before its
+// range from phys_own (a few KB) instead of waiting for another block.
+struct PushArgs {
+  const int* phys_own;                 // [S, K]
+  const __nv_bfloat16* x;              // [S, H]
+  PeerTable stage;                     // rank p's staging buffer base [W, S, H]
+  PeerTable flags;                     // rank p's push-arrival words [W]
+  int S, K, H, nlp, rank, world;
+  const unsigned long long* epoch_ptr;
+  unsigned int* counter;
+  unsigned long long* status;
+};
+
+__global__ void __launch_bounds__(256) dispatch_push_kernel(PushArgs a) {
+  __shared__ int before[kMaxRanks];      // tokens before this block's range that go to rank d
+  __shared__ unsigned long long tmask[64];
+  const unsigned long long epoch = step_epoch(a.epoch_ptr, false);
+  const int tpb = (a.S + gridDim.x - 1) / gridDim.x;          // tokens per block (<= 64)
+  const int t_lo = blockIdx.x * tpb;
+  const int t_hi = min(a.S, t_lo + tpb);
+  for (int d = threadIdx.x; d < a.world; d += blockDim.x) before[d] = 0;
+  __syncthreads();
+  // owner masks of all tokens below t_hi: count those before the range, keep those inside it
+  for (int t = threadIdx.x; t < t_hi; t += blockDim.x) {
+    unsigned long long m = 0;
+    for (int k = 0; k < a.K; ++k) {
+      const int p = a.phys_own[t * a.K + k];
+      if (p >= 0) m |= 1ull << (p / a.nlp);
+    }
+    if (t < t_lo) {
+      while (m) { const int d = __ffsll((long long)m) - 1; m &= m - 1; atomicAdd(&before[d], 1); }
+    } else {
+      tmask[t - t_lo] = m;
+    }
+  }
+  __syncthreads();
+  // one warp per (token, destination) row
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int vec_per_row = a.H / 8;
+  const size_t region = (size_t)a.rank * a.S * a.H;
+  for (int pair = wid; pair < (t_hi - t_lo) * a.world; pair += nw) {
+    const int tl = pair / a.world, d = pair - tl * a.world;
+    const unsigned long long m = tmask[tl];
+    if (!((m >> d) & 1ull)) continue;
+    int slot = before[d];
+    for (int q = 0; q < tl; ++q) slot += (int)((tmask[q] >> d) & 1ull);
+    const uint4* sp = reinterpret_cast<const uint4*>(a.x + (size_t)(t_lo + tl) * a.H);
+    uint4* dp = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.stage.ptr[d]) + region + (size_t)slot * a.H);
+    for (int v0 = 0; v0 < vec_per_row; v0 += 256) {
+      uint4 buf[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const int v = v0 + q * 32 + lane;
+        if (v < vec_per_row) buf[q] = sp[v];
+      }
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const int v = v0 + q * 32 + lane;
+        if (v < vec_per_row) dp[v] = buf[q];
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const unsigned int prev = atomicInc(a.counter, gridDim.x - 1);
+    if (prev == gridDim.x - 1) {
+      __threadfence_system();
+      for (int p = 0; p < a.world; ++p)
+        st_relaxed_sys(reinterpret_cast<unsigned long long*>(a.flags.ptr[p]) + a.rank, epoch);
+    }
+  }
+}
+
 struct MoveArgs {
   const int* m_this;                       // [2] rows, first global row
   const int* row_tok;                      // [cap]
@@ -150,7 +231,10 @@ __global__ void combine_reduce_kernel(const __nv_bfloat16* __restrict__ panel, _
     for (int q = 0; q < 4; ++q) o2[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
     reinterpret_cast<uint4*>(y + t * H)[v] = out;
   }
-  if (threadIdx.x == 0) trace_mark_max(status, TR_REDUCE_END);
+  if (threadIdx.x == 0) {
+    trace_mark_max(status, TR_REDUCE_END);
+    trace_mark_max(status, TR_RING + 16 + (int)(epoch & 15));
+  }
 }
 
 }  // namespace zepp

@@ -60,6 +60,7 @@ struct MetaArgs {
   long long* row_dst;       // [recv_cap]
   float* row_scale;         // [recv_cap]
   int hidden;               // H (row_dst is an element offset into the home's [S*K, H] panel)
+  int staged;               // 1: row_tok holds (source, staging slot) instead of (source, token)
   const int* group_order;   // [gpe] schedule word per group (bit 30 = moved-in slot: its tiles go last) or nullptr
   // exchange wait
   const unsigned long long* routing_flags;
@@ -490,13 +491,33 @@ __global__ void __launch_bounds__(kMetaThreads) meta_pass2_kernel(MetaArgs a) {
     }
   }
   __syncthreads();
+  // staged dispatch: the source stored each token once per destination rank at slot = number of its
+  // earlier tokens that also go to that rank; the same slot follows here from the per-tile unique
+  // counts (tiles hold whole tokens) and a scan over the tile's tokens
+  __shared__ int s_tokslot[kMetaThreads];
+  __shared__ int s_warp_tot[33];
+  if (a.staged && a.row_tok != nullptr) {
+    const int tpt = a.tokens_per_tile;
+    for (int t = threadIdx.x; t < tpt; t += blockDim.x) s_tokslot[t] = 0;
+    __syncthreads();
+    if (valid && e / a.gpe == a.my_rank) s_tokslot[threadIdx.x / a.K] = 1;
+    __syncthreads();
+    const int f = threadIdx.x < tpt ? s_tokslot[threadIdx.x] : 0;
+    int total;
+    int pre = block_exclusive_scan(f, s_warp_tot, &total);
+    const int ucw = a.R + a.R / a.L;
+    for (int q = 0; q < tb; ++q) pre += a.tile_uc[(size_t)(src * a.tiles_per_src + q) * ucw + a.my_rank];
+    __syncthreads();
+    if (threadIdx.x < tpt) s_tokslot[threadIdx.x] = pre;
+    __syncthreads();
+  }
   if (!valid) return;
   const int idx = wc[wid * E_virt + e] + __popc(m & ((1u << lane) - 1u));
   a.scatter_index[flat] = idx;
   if (a.row_tok != nullptr && e / a.gpe == a.my_rank) {
     const int r = idx - a.m_this[1];
     if (r >= 0 && r < a.recv_cap) {
-      a.row_tok[r] = src * a.S + n / a.K;
+      a.row_tok[r] = src * a.S + (a.staged ? s_tokslot[threadIdx.x / a.K] : n / a.K);
       a.row_scale[r] = a.probs_all ? a.probs_all[flat] : 1.0f;
       a.row_dst[r] = ((long long)src << 40) | ((long long)n * a.hidden);
     }

@@ -510,8 +510,11 @@ __global__ void slot_table_kernel(const int* l2p, const int* lcnts, int G, int R
 }
 
 __global__ void __launch_bounds__(256) route_simple_publish_kernel(SimpleRouteArgs a) {
-  if (blockIdx.x == 0 && threadIdx.x == 0) trace_mark(a.status, TR_ROUTE);
   const unsigned long long epoch = step_epoch(a.ctr, a.first != 0);
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    trace_mark(a.status, TR_ROUTE);
+    trace_mark(a.status, TR_RING + (int)(epoch & 15));
+  }
   extern __shared__ int slots[];             // [G] staged copy of the slot table (routing blocks)
   if ((int)blockIdx.x < a.route_blocks) {
     for (int g = threadIdx.x; g < a.G; g += blockDim.x) slots[g] = a.slot_of[g];

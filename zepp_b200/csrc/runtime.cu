@@ -5,6 +5,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <new>
@@ -206,6 +207,8 @@ struct zepp_layer {
   int* xchg_all[2];                  // [R, 2*SK]
   unsigned long long *loads_flags, *routing_flags, *x_flags, *done_flags;   // [R] each
   __nv_bfloat16* xsym[2];            // [S, H]
+  __nv_bfloat16* stage = nullptr;    // [W, S, H] staged dispatch rows, region s written by rank s
+  unsigned long long* push_flags = nullptr;   // [R]
   __nv_bfloat16* panel;              // [S*K, H]
   // local buffers
   __nv_bfloat16 *recv, *act, *staging;
@@ -223,6 +226,8 @@ struct zepp_layer {
   unsigned long long* status;
   // device pointer tables
   const __nv_bfloat16** x_ptrs[2];
+  const __nv_bfloat16** stage_ptrs = nullptr;   // [W] this rank's staging regions (one per source)
+  PeerTable stage_dst, push_flag_dst;
   __nv_bfloat16** panels;
   unsigned long long** done_ptrs;
   // host peer tables for the publishing kernels
@@ -253,7 +258,8 @@ extern "C" size_t zepp_layer_arena_bytes(const zepp_layer_cfg* c) {
   const size_t SK = S * K, nlp = G / R + c->redundant_slots_per_rank, gpe = nlp + 1, E = R * gpe, cap = c->caps[0];
   const size_t tiles = (SK + 1023) / 1024 + 1;
   size_t b = 0;
-  b += 2 * al(R * G * 4) + 2 * al(R * 2 * SK * 4) + 4 * al(R * 8) + 2 * al(S * H * 2) + al(SK * H * 2);
+  b += 2 * al(R * G * 4) + 2 * al(R * 2 * SK * 4) + 6 * al(R * 8) + 2 * al(S * H * 2) + al(SK * H * 2);
+  if (R > 1 && c->strategy == 0) b += al(R * S * H * 2);
   b += al(cap * H * 2) * 2 + al(cap * I * 2);
   b += 4 * al(SK * 4) + al(2 * SK * 4) + al((size_t)zepp_route_workspace_ints((int)G, (int)R) * 4);
   b += 3 * al(R * nlp * 4) + 2 * al(G * R * 4) + al(G * 4);
@@ -286,6 +292,8 @@ static int layer_alloc(zepp_layer* l) {
   LA(l->done_flags, R);
   for (int b = 0; b < 2; ++b) LA(l->xsym[b], (size_t)l->S * l->H);
   LA(l->panel, (size_t)l->SK * l->H);
+  LA(l->push_flags, R);
+  if (R > 1 && l->cfg.strategy == 0) LA(l->stage, (size_t)R * l->S * l->H);
   // local part
   LA(l->recv, (size_t)l->cap * l->H);
   LA(l->act, (size_t)l->cap * l->I);
@@ -333,6 +341,7 @@ static int layer_alloc(zepp_layer* l) {
   LA(l->status, ST_WORDS);
   LA(l->step_ctr, 2);
   for (int b = 0; b < 2; ++b) LA(l->x_ptrs[b], R);
+  LA(l->stage_ptrs, R);
   LA(l->panels, R);
   LA(l->done_ptrs, R);
   return 0;
@@ -382,8 +391,14 @@ extern "C" int zepp_layer_create(zepp_rt* rt, const zepp_layer_cfg* c, zepp_laye
     l->loads_flag_dst.ptr[p] = peer_ptr(rt, p, l->loads_flags);
     l->routing_flag_dst.ptr[p] = peer_ptr(rt, p, l->routing_flags);
     l->x_flag_dst.ptr[p] = peer_ptr(rt, p, l->x_flags);
+    l->push_flag_dst.ptr[p] = peer_ptr(rt, p, l->push_flags);
+    l->stage_dst.ptr[p] = l->stage ? (void*)peer_ptr(rt, p, l->stage) : nullptr;
     pp[p] = peer_ptr(rt, p, l->panel);
     dp[p] = peer_ptr(rt, p, l->done_flags);
+  }
+  if (l->stage) {
+    for (int p = 0; p < R; ++p) xp[p] = l->stage + (size_t)p * l->S * l->H;
+    CU_OK(cudaMemcpy(l->stage_ptrs, xp.data(), R * sizeof(void*), cudaMemcpyHostToDevice));
   }
   CU_OK(cudaMemcpy(l->panels, pp.data(), R * sizeof(void*), cudaMemcpyHostToDevice));
   CU_OK(cudaMemcpy(l->done_ptrs, dp.data(), R * sizeof(void*), cudaMemcpyHostToDevice));
@@ -399,6 +414,10 @@ extern "C" int zepp_layer_create(zepp_rt* rt, const zepp_layer_cfg* c, zepp_laye
   CU_OK(cudaFuncSetAttribute(moe_gemm_kernel<MODE_DOWN_COMBINE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              GemmCfg<MODE_DOWN_COMBINE>::kSmemBytes));
   if (pass2_prepare(pass2_smem(l->tokens_per_tile, l->K, l->E_virt))) { delete l; return 1; }
+  {
+    const char* g = getenv("ZEPP_B200_GRAPHS");     // "0": launch the step's kernels one by one instead of as a graph
+    if (g != nullptr && g[0] == '0') l->use_graphs = false;
+  }
   if (meta_smem(l->W, l->NN, l->E_virt) > 48 * 1024) { delete l; return fail("too many ranks / experts for the metadata kernels"); }
   *out = l;
   return 0;
@@ -465,6 +484,7 @@ static MetaArgs layer_meta_args(zepp_layer* l) {
   m.tile_ready = l->tile_ready; m.max_tiles = l->max_tiles; m.recv_cap = l->cap; m.m_this = l->m_this;
   m.row_tok = l->row_tok; m.row_dst = l->row_dst; m.row_scale = l->row_scale; m.hidden = l->H;
   m.group_order = nullptr;
+  m.staged = l->stage != nullptr ? 1 : 0;
   m.routing_flags = l->W > 1 ? l->routing_flags : nullptr;
   m.epoch_ptr = l->step_ctr; m.limit_ns = l->rt->wait_ns; m.status = l->status;
   m.block_counter = l->counters + 8;
@@ -615,6 +635,9 @@ static GemmArgs layer_gemm_args(zepp_layer* l, bool first) {
   g.row_tok = l->row_tok; g.x_ptrs = l->x_ptrs[0]; g.x_ptrs_odd = l->x_ptrs[1];
   g.x_self = (const __nv_bfloat16*)l->x_self;
   g.x_flags = l->W > 1 ? l->x_flags : nullptr;
+  if (l->stage != nullptr) {       // staged dispatch: rows were pushed into this rank's staging regions
+    g.x_ptrs = l->stage_ptrs; g.x_ptrs_odd = l->stage_ptrs; g.x_self = nullptr; g.x_flags = l->push_flags;
+  }
   g.recv = l->recv; g.tile_ready = l->tile_ready; g.tokens_per_rank = l->S; g.gather = 0;
   g.status = l->status; g.mbar_limit = 1u << 24; g.flag_limit_ns = l->rt->wait_ns;
   return g;
@@ -659,6 +682,18 @@ extern "C" int zepp_layer_forward_phase(zepp_layer* l, int phase, const void* x,
     l->x_self = x;
     if (l->x_fused == x && x != nullptr) {     // already published by the routing kernel of this step
       l->x_fused = nullptr;
+      return 0;
+    }
+    if (l->stage != nullptr) {
+      PushArgs pa{};
+      pa.phys_own = l->phys_own; pa.x = (const __nv_bfloat16*)x; pa.stage = l->stage_dst; pa.flags = l->push_flag_dst;
+      pa.S = l->S; pa.K = l->K; pa.H = l->H; pa.nlp = l->nlp; pa.rank = l->rt->rank; pa.world = l->W;
+      pa.epoch_ptr = l->step_ctr; pa.counter = l->counters + 10; pa.status = l->status;
+      int grid = 2 * l->rt->sm_count;
+      if (grid > l->S) grid = l->S;
+      if (grid * 64 < l->S) grid = (l->S + 63) / 64;
+      dispatch_push_kernel<<<grid, 256, 0, st>>>(pa);
+      LAUNCH_OK();
       return 0;
     }
     if (l->W > 1) {
@@ -716,10 +751,10 @@ extern "C" int zepp_layer_forward(zepp_layer* l, const void* x, void* y, void* s
 // One whole step in launch order.  x is published right after the first planning kernel, long before
 // the dispatch GEMM of any rank needs it, so the GEMM's wait for x never stalls on rank skew.
 static int step_enqueue(zepp_layer* l, const int32_t* ids, const float* wts, const void* x, void* y, void* stream) {
-  l->fuse_x = (!needs_loads(l) && l->c_max <= 1) ? x : nullptr;
+  l->fuse_x = (!needs_loads(l) && l->c_max <= 1 && l->stage == nullptr) ? x : nullptr;
   l->x_fused = nullptr;
   if (zepp_layer_prepare_phase(l, 0, ids, wts, stream)) return 1;
-  if (needs_loads(l)) {
+  if (needs_loads(l) && l->stage == nullptr) {
     if (zepp_layer_forward_phase(l, 0, x, y, stream)) return 1;
     if (zepp_layer_prepare_phase(l, 1, ids, wts, stream)) return 1;
   } else {
@@ -799,7 +834,7 @@ extern "C" int zepp_layer_status(zepp_layer* l, void* stream, uint64_t out[8]) {
   return 0;
 }
 
-extern "C" int zepp_layer_trace(zepp_layer* l, void* stream, uint64_t out[32]) {
+extern "C" int zepp_layer_trace(zepp_layer* l, void* stream, uint64_t out[64]) {
   CU_OK(cudaSetDevice(l->rt->device));
   CU_OK(cudaStreamSynchronize((cudaStream_t)stream));
   CU_OK(cudaMemcpy(out, l->status, ST_WORDS * 8, cudaMemcpyDeviceToHost));

@@ -223,6 +223,15 @@ class EPMoE(torch.nn.Module):
         t0 = t[0]
         return {n: (v - t0) / 1e3 if v else None for n, v in zip(self.TRACE_NAMES, t)}
 
+    def step_ring(self):
+        """(start, end) device stamps in microseconds of the last 16 steps, oldest first, relative to the oldest start."""
+        t = self._h.trace()
+        pairs = sorted((t[32 + i], t[48 + i]) for i in range(16) if t[32 + i])
+        if not pairs:
+            return []
+        t0 = pairs[0][0]
+        return [((a - t0) / 1e3, (b - t0) / 1e3) for a, b in pairs]
+
     def tables(self, *names):
         """Planner products of the last prepare (device tensors): see runtime.TABLES."""
         return [self._h.table(n) for n in names]

@@ -137,7 +137,7 @@ class LayerHandle:
         return [int(v) for v in out]
 
     def trace(self):
-        out = (ctypes.c_uint64 * 32)()
+        out = (ctypes.c_uint64 * 64)()
         check(lib().zepp_layer_trace(self.h, self._stream(), out))
         return [int(v) for v in out]
 
