@@ -60,10 +60,16 @@ int zepp_layer_set_placement(zepp_layer* layer, const int32_t* p2l, const int32_
 /* OverlapComm.set_weights (python/zepp/comm/overlap.py:95-100): w1 [gpe, ffn1, H], w2 [gpe, H, ffn] bf16 */
 int zepp_layer_set_weights(zepp_layer* layer, const void* w1_dev, const void* w2_dev);
 
-/* EPMoE.prepare (python/zepp/layer.py:145-171): loads exchange -> (swap decision) -> route ->
- * routing exchange -> routed metadata, all on the device.  Phases: 0 loads, 1 route, 2 metadata;
- * zepp_layer_prepare runs all three (ranks in separate processes); linked single-process ranks call
- * one phase for every rank before the next phase. */
+/* WeightSlots (python/zepp/swap.py:236-300): with swap on, the layer owns the peer-visible weight slots
+ * w1 [gpe, ffn1, H], w2 [gpe, H, ffn] that swapped experts travel between; callers fill them in place (or
+ * pass their own tensors to zepp_layer_set_weights, which copies them in). */
+int zepp_layer_weight_slots(zepp_layer* layer, void** w1_dev, void** w2_dev);
+
+/* EPMoE.prepare (python/zepp/layer.py:145-171): loads exchange -> (swap decision + weight movement) ->
+ * route -> routing exchange -> routed metadata, all on the device.  Phases: 0 loads, 1 swap decision and
+ * pull of incoming experts (no-op with swap off), 2 commit of the pulled experts + route, 3 metadata;
+ * zepp_layer_prepare runs all four (ranks in separate processes); linked single-process ranks call one
+ * phase for every rank before the next phase. */
 int zepp_layer_prepare(zepp_layer* layer, const int32_t* topk_ids_dev, const float* topk_weights_dev, void* stream);
 int zepp_layer_prepare_phase(zepp_layer* layer, int phase, const int32_t* topk_ids_dev,
                              const float* topk_weights_dev, void* stream);

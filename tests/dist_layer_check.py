@@ -18,6 +18,7 @@ def main():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--tokens", type=int, default=64)
     ap.add_argument("--ranks-per-node", type=int, default=0)
+    ap.add_argument("--swap", type=int, default=0)
     a = ap.parse_args()
     from oracle import layer as ol
     from zepp_b200 import EPMoE, EPMoEConfig, ModelShape
@@ -30,9 +31,9 @@ def main():
     shape = ModelShape(32, 8, 512, 256, act="swiglu")
     S = a.tokens
     cfg = EPMoEConfig(shape=shape, ranks=world, ranks_per_node=a.ranks_per_node or world, max_tokens_per_rank=S,
-                      comm_strategy=a.strategy)
+                      comm_strategy=a.strategy, swap=bool(a.swap))
     gen = torch.Generator().manual_seed(5)
-    p = wl.popularity(shape.num_experts, 1.0, gen)
+    p = wl.popularity(shape.num_experts, 1.2 if a.swap else 1.0, gen)
     ids, wts = wl.routing(world, S, shape.topk, p, gen)
     layer = EPMoE(cfg, dist.group.WORLD, ids, ids)
     W1 = torch.stack([wl.expert_w1(e, shape) for e in range(shape.num_experts)])
@@ -55,9 +56,10 @@ def main():
         err = float((y.float().cpu() - ref).abs().max())
         worst = max(worst, err)
         ok &= bool(torch.allclose(y.float().cpu(), ref, rtol=2e-2, atol=2e-2))
+    moves = layer.swap_moves if a.swap else 0
     flag = torch.tensor([0 if ok else 1], device="cuda")
     dist.all_reduce(flag)
-    print(f"[dist_layer_check] rank {rank}/{world} {a.strategy}: {'PASS' if ok else 'FAIL'} max|err| {worst:.4g}", flush=True)
+    print(f"[dist_layer_check] rank {rank}/{world} {a.strategy}: {'PASS' if ok else 'FAIL'} max|err| {worst:.4g} swap moves (last step) {moves}", flush=True)
     layer.close()
     dist.barrier()
     dist.destroy_process_group()

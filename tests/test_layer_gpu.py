@@ -195,3 +195,52 @@ def test_benchmark_shape_one_rank_of_eight():
     """Qwen3-30B layer shape, 8-way sharding emulated on one GPU at 64 tokens per rank (full H, I, E)."""
     shape = dataclasses.replace(wl.shape_of("qwen3-30b"))
     _run_local(shape, 8, 8, 64, "overlap", steps=1, check_plan=False)
+
+
+def test_swap_moves_weights_and_routes_on_the_new_placement():
+    """swap=True on 8 emulated ranks with skewed routing: the device decision equals the host oracle's, the
+    placement tables change, the moved experts' weights follow them, and outputs stay within tolerance on the
+    swap step and on the steps after it."""
+    shape, W, S = MID, 8, 64
+    cfg = EPMoEConfig(shape=shape, ranks=W, ranks_per_node=W, max_tokens_per_rank=S, swap=True)
+    gen = torch.Generator().manual_seed(4)
+    p = wl.popularity(shape.num_experts, 1.2, gen)
+    ids, wts = wl.routing(W, S, shape.topk, p, gen)
+    layers, rts = make_local_layers(cfg, ids, ids, wait_limit_ms=500)
+    W1, W2 = _weights(shape)
+    for l in layers:
+        l.load_weights(lambda e: W1[e], lambda e: W2[e])
+    pl0 = layers[0].placement
+    cur = op.Placement(pl0.p2l.numpy().copy(), pl0.l2p.numpy().copy(), pl0.lcnts.numpy())
+    total_moves = 0
+    try:
+        for step in range(3):
+            if step == 2:
+                p = wl.drift(p, 0.5, gen)
+            if step:
+                ids, wts = wl.routing(W, S, shape.topk, p, gen)
+            xs = [wl.tokens(r, S, shape.hidden, seed=step) for r in range(W)]
+            ys = local_step(layers, [ids[r].cuda() for r in range(W)], [wts[r].cuda() for r in range(W)],
+                            [x.cuda() for x in xs])
+            for l in layers:
+                l.check()
+            load_g = np.bincount(ids.numpy().reshape(-1), minlength=shape.num_experts)
+            new, rounds = op.decide_swaps(load_g, cur, W, cfg.slots_per_rank, cfg.router_c)
+            if rounds:
+                moves = op.net_moves(cur.p2l, new, W, cfg.slots_per_rank)
+                total_moves += sum(len(m) for m in moves)
+                cur = op.Placement(new, op.rebuild_l2p(new, shape.num_experts, W), cur.lcnts)
+                assert layers[0].swap_moves == sum(len(m) for m in moves)
+            else:
+                assert layers[0].swap_moves == 0
+            for l in layers:
+                assert np.array_equal(l.tables("p2l")[0].cpu().numpy(), cur.p2l), step
+            refs = _reference(xs, ids, wts, W1, W2)
+            for r in range(W):
+                _close(ys[r], refs[r], f"swap step {step} rank {r}")
+        assert total_moves > 0, "the skewed routing never triggered a swap"
+    finally:
+        for l in layers:
+            l.close()
+        for rt in rts:
+            rt.destroy()

@@ -37,3 +37,14 @@ def test_layer_across_gpus(strategy):
     r = _run(nproc, "--strategy", strategy)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert r.stdout.count("PASS") == nproc, r.stdout[-3000:]
+
+
+def test_layer_across_gpus_with_swap():
+    """Expert swap across real GPUs: moved experts' weights are pulled over NVLink from the source rank's slots."""
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    nproc = 2 if n < 4 else (4 if n < 8 else 8)
+    r = _run(nproc, "--strategy", "overlap", "--swap", "1", "--steps", "4")
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("PASS") == nproc, r.stdout[-3000:]

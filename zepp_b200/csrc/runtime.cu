@@ -226,6 +226,11 @@ struct zepp_layer {
   unsigned long long* status;
   // device pointer tables
   const __nv_bfloat16** x_ptrs[2];
+  // swap: weight slots owned by the layer (peer-visible), staging for incoming experts, pulled flags
+  __nv_bfloat16 *w1_slots = nullptr, *w2_slots = nullptr, *stag1 = nullptr, *stag2 = nullptr;
+  unsigned long long* swap_flags = nullptr;
+  const uint4 **w1_peers = nullptr, **w2_peers = nullptr;
+  PeerTable swap_flag_dst;
   const __nv_bfloat16** stage_ptrs = nullptr;   // [W] this rank's staging regions (one per source)
   PeerTable stage_dst, push_flag_dst;
   __nv_bfloat16** panels;
@@ -260,6 +265,7 @@ extern "C" size_t zepp_layer_arena_bytes(const zepp_layer_cfg* c) {
   size_t b = 0;
   b += 2 * al(R * G * 4) + 2 * al(R * 2 * SK * 4) + 6 * al(R * 8) + 2 * al(S * H * 2) + al(SK * H * 2);
   if (R > 1 && c->strategy == 0) b += al(R * S * H * 2);
+  if (c->swap) b += (gpe + 8) * (al((c->act == 1 ? 2 : 1) * I * H * 2) + al(H * I * 2)) + (1 << 20);
   b += al(cap * H * 2) * 2 + al(cap * I * 2);
   b += 4 * al(SK * 4) + al(2 * SK * 4) + al((size_t)zepp_route_workspace_ints((int)G, (int)R) * 4);
   b += 3 * al(R * nlp * 4) + 2 * al(G * R * 4) + al(G * 4);
@@ -293,6 +299,11 @@ static int layer_alloc(zepp_layer* l) {
   for (int b = 0; b < 2; ++b) LA(l->xsym[b], (size_t)l->S * l->H);
   LA(l->panel, (size_t)l->SK * l->H);
   LA(l->push_flags, R);
+  LA(l->swap_flags, R);
+  if (l->cfg.swap) {
+    LA(l->w1_slots, (size_t)l->gpe * l->ffn1 * l->H);
+    LA(l->w2_slots, (size_t)l->gpe * l->H * l->I);
+  }
   if (R > 1 && l->cfg.strategy == 0) LA(l->stage, (size_t)R * l->S * l->H);
   // local part
   LA(l->recv, (size_t)l->cap * l->H);
@@ -342,6 +353,12 @@ static int layer_alloc(zepp_layer* l) {
   LA(l->step_ctr, 2);
   for (int b = 0; b < 2; ++b) LA(l->x_ptrs[b], R);
   LA(l->stage_ptrs, R);
+  if (l->cfg.swap) {
+    LA(l->stag1, (size_t)8 * l->ffn1 * l->H);
+    LA(l->stag2, (size_t)8 * l->H * l->I);
+    LA(l->w1_peers, R);
+    LA(l->w2_peers, R);
+  }
   LA(l->panels, R);
   LA(l->done_ptrs, R);
   return 0;
@@ -392,9 +409,17 @@ extern "C" int zepp_layer_create(zepp_rt* rt, const zepp_layer_cfg* c, zepp_laye
     l->routing_flag_dst.ptr[p] = peer_ptr(rt, p, l->routing_flags);
     l->x_flag_dst.ptr[p] = peer_ptr(rt, p, l->x_flags);
     l->push_flag_dst.ptr[p] = peer_ptr(rt, p, l->push_flags);
+    l->swap_flag_dst.ptr[p] = peer_ptr(rt, p, l->swap_flags);
     l->stage_dst.ptr[p] = l->stage ? (void*)peer_ptr(rt, p, l->stage) : nullptr;
     pp[p] = peer_ptr(rt, p, l->panel);
     dp[p] = peer_ptr(rt, p, l->done_flags);
+  }
+  if (l->cfg.swap) {
+    std::vector<const uint4*> wp(R);
+    for (int p = 0; p < R; ++p) wp[p] = (const uint4*)peer_ptr(rt, p, l->w1_slots);
+    CU_OK(cudaMemcpy(l->w1_peers, wp.data(), R * sizeof(void*), cudaMemcpyHostToDevice));
+    for (int p = 0; p < R; ++p) wp[p] = (const uint4*)peer_ptr(rt, p, l->w2_slots);
+    CU_OK(cudaMemcpy(l->w2_peers, wp.data(), R * sizeof(void*), cudaMemcpyHostToDevice));
   }
   if (l->stage) {
     for (int p = 0; p < R; ++p) xp[p] = l->stage + (size_t)p * l->S * l->H;
@@ -451,7 +476,22 @@ extern "C" int zepp_layer_set_placement(zepp_layer* l, const int32_t* p2l, const
   return 0;
 }
 
+extern "C" int zepp_layer_weight_slots(zepp_layer* l, void** w1, void** w2) {
+  if (!l->cfg.swap) return fail("weight_slots: the layer owns weight slots only with swap on");
+  *w1 = l->w1_slots;
+  *w2 = l->w2_slots;
+  return 0;
+}
+
 extern "C" int zepp_layer_set_weights(zepp_layer* l, const void* w1, const void* w2) {
+  if (l->cfg.swap) {
+    // swapped experts travel between ranks: the weights live in the layer's peer-visible slots
+    CU_OK(cudaSetDevice(l->rt->device));
+    if (w1 != l->w1_slots) CU_OK(cudaMemcpy(l->w1_slots, w1, (size_t)l->gpe * l->ffn1 * l->H * 2, cudaMemcpyDeviceToDevice));
+    if (w2 != l->w2_slots) CU_OK(cudaMemcpy(l->w2_slots, w2, (size_t)l->gpe * l->H * l->I * 2, cudaMemcpyDeviceToDevice));
+    w1 = l->w1_slots;
+    w2 = l->w2_slots;
+  }
   if (make_map(&l->tm_w1, w1, (uint64_t)l->gpe * l->ffn1, l->H, 128)) return 1;
   if (make_map(&l->tm_w2, w2, (uint64_t)l->gpe * l->H, l->I, 128)) return 1;
   for (auto& gph : l->graphs) cudaGraphExecDestroy(gph.exec);     // the tensor maps are baked into captured launches
@@ -508,6 +548,21 @@ static int pass2_prepare(size_t bytes) {
   return 0;
 }
 
+__global__ void flags_wait_kernel(const unsigned long long* flags, int world, const unsigned long long* epoch_ptr,
+                                  unsigned long long limit_ns, unsigned long long* status, int what) {
+  block_wait_all(flags, world, step_epoch(epoch_ptr, false), limit_ns, status, what);
+}
+
+static SwapMoveArgs layer_swap_args(zepp_layer* l) {
+  SwapMoveArgs a{};
+  a.block = l->swap_block; a.R = l->W; a.rank = l->rt->rank; a.cap = 8; a.world = l->W;
+  a.w1_vec = (size_t)l->ffn1 * l->H / 8; a.w2_vec = (size_t)l->H * l->I / 8;
+  a.w1 = (uint4*)l->w1_slots; a.w2 = (uint4*)l->w2_slots; a.w1_peers = l->w1_peers; a.w2_peers = l->w2_peers;
+  a.stag1 = (uint4*)l->stag1; a.stag2 = (uint4*)l->stag2; a.flags = l->swap_flag_dst; a.my_flags = l->swap_flags;
+  a.epoch_ptr = l->step_ctr; a.limit_ns = l->rt->wait_ns; a.counter = l->counters + 12; a.status = l->status;
+  return a;
+}
+
 // Does this step need the gathered loads?  Only the water-fill (some expert has more than one
 // replica) and the swap decision consume them.
 static bool needs_loads(const zepp_layer* l) { return l->c_max > 1 || l->cfg.swap != 0; }
@@ -530,24 +585,42 @@ extern "C" int zepp_layer_prepare_phase(zepp_layer* l, int phase, const int32_t*
     return 0;
   }
   if (phase == 1) {
+    if (!l->cfg.swap) return 0;
+    // swap: decision on the gathered loads (rewrites p2l / l2p on the device), lane metadata, and the
+    // pull of this rank's incoming experts into staging; nothing is read on the host
+    const double C = (double)l->cfg.c_num / (double)l->cfg.c_den;
+    flags_wait_kernel<<<1, 64, 0, st>>>(R > 1 ? l->loads_flags : nullptr, R, l->step_ctr, l->rt->wait_ns, l->status, WAIT_LOADS);
+    LAUNCH_OK();
+    const int b = (int)(l->epoch & 1);
+    if (zepp_swap_decide(l->loads_all[b], l->p2l, l->l2p, l->lcnts, R, l->G, l->L, l->nlp, C, 8, 32,
+                         (int64_t*)l->swap_block, stream))
+      return 1;
+    l->launches++;
+    CU_OK(cudaMemsetAsync(l->sched, 0, l->gpe * 4, st));
+    if (zepp_lane_arm((const int64_t*)l->swap_block, R, me, l->nlp, 8, (int64_t*)l->gate, l->sched, (int64_t*)l->ovr0,
+                      (int64_t*)l->ovr1, (const int64_t*)l->stag, (int64_t)l->epoch, stream))
+      return 1;
+    l->launches++;
+    SwapMoveArgs sm = layer_swap_args(l);
+    swap_pull_kernel<<<l->rt->sm_count * 2, 256, 0, st>>>(sm);
+    LAUNCH_OK();
+    return 0;
+  }
+  if (phase == 2) {
     if (ids) { l->ids_in = ids; l->wts_in = wts; }
+    if (l->cfg.swap) {
+      SwapMoveArgs sm = layer_swap_args(l);
+      swap_commit_kernel<<<l->rt->sm_count * 2, 256, 0, st>>>(sm);
+      LAUNCH_OK();
+      slot_table_kernel<<<(l->G + 127) / 128, 128, 0, st>>>(l->l2p, l->lcnts, l->G, l->W, l->slot_of);
+      LAUNCH_OK();
+    }
     if (l->c_max <= 1) {
       SimpleRouteArgs sa{};
       sa.topk_own = l->ids_in; sa.probs_own = l->wts_in; sa.slot_of = l->slot_of;
       sa.SK = l->SK; sa.G = l->G; sa.R = R; sa.my_rank = me; sa.world = R; sa.first = needs_loads(l) ? 0 : 1;
       sa.phys_own = l->phys_own; sa.send_row = l->send_row; sa.dst = l->xchg_dst[0]; sa.dst_odd = l->xchg_dst[1];
       sa.flags = l->routing_flag_dst; sa.ctr = l->step_ctr; sa.block_counter = l->counters + 0; sa.status = l->status;
-      if (l->cfg.swap) {
-        // the decision reads the gathered loads: wait for them with the generic router's table pass
-        RouteArgs ra{};
-        ra.topk_own = nullptr; ra.n_entries = 0; ra.loads = l->loads_all[0]; ra.loads_odd = l->loads_all[1];
-        ra.l2p = l->l2p; ra.lcnts = l->lcnts; ra.G = l->G; ra.R = R; ra.L = l->L; ra.nlp = l->nlp; ra.my_rank = me;
-        ra.c_num = l->cfg.c_num; ra.c_den = l->cfg.c_den; ra.ws = l->route_ws; ra.phys_own = l->phys_own;
-        ra.loads_flags = R > 1 ? l->loads_flags : nullptr; ra.epoch_ptr = l->step_ctr; ra.limit_ns = l->rt->wait_ns;
-        ra.status = l->status; ra.stats = l->route_stats;
-        route_kernel<<<(l->G + 7) / 8, 256, 0, st>>>(ra);
-        LAUNCH_OK();
-      }
       sa.route_blocks = (l->SK / 4 + 255) / 256 > 0 ? (l->SK / 4 + 255) / 256 : 1;
       if ((l->SK & 3) != 0) sa.route_blocks = (l->SK + 255) / 256;
       int grid = sa.route_blocks;
@@ -584,26 +657,9 @@ extern "C" int zepp_layer_prepare_phase(zepp_layer* l, int phase, const int32_t*
       route_finish_kernel<<<8, 256, 0, st>>>(fa);
       LAUNCH_OK();
     }
-    if (l->cfg.swap) {
-      // decision + lane metadata on scratch copies of the tables (the decision is reported in the
-      // result block; the resident placement changes only through zepp_layer_set_placement)
-      const int b = (int)(l->epoch & 1);
-      CU_OK(cudaMemcpyAsync(l->p2l_try, l->p2l, (size_t)R * l->nlp * 4, cudaMemcpyDeviceToDevice, st));
-      CU_OK(cudaMemcpyAsync(l->l2p_try, l->l2p, (size_t)l->G * R * 4, cudaMemcpyDeviceToDevice, st));
-      const double C = (double)l->cfg.c_num / (double)l->cfg.c_den;
-      if (zepp_swap_decide(l->loads_all[b], l->p2l_try, l->l2p_try, l->lcnts, R, l->G, l->L, l->nlp, C, 8, 32,
-                           (int64_t*)l->swap_block, stream))
-        return 1;
-      l->launches++;
-      CU_OK(cudaMemsetAsync(l->sched, 0, l->gpe * 4, st));
-      if (zepp_lane_arm((const int64_t*)l->swap_block, R, me, l->nlp, 8, (int64_t*)l->gate, l->sched,
-                        (int64_t*)l->ovr0, (int64_t*)l->ovr1, (const int64_t*)l->stag, (int64_t)l->epoch, stream))
-        return 1;
-      l->launches++;
-    }
     return 0;
   }
-  if (phase == 2) {
+  if (phase == 3) {
     MetaArgs m = layer_meta_args(l);
     const int grid = R * l->tiles_per_src;
     meta_pass1_kernel<<<grid, kMetaThreads, meta_smem(R, l->NN, l->E_virt), st>>>(m);      // + scan in its last block
@@ -616,7 +672,7 @@ extern "C" int zepp_layer_prepare_phase(zepp_layer* l, int phase, const int32_t*
 }
 
 extern "C" int zepp_layer_prepare(zepp_layer* l, const int32_t* ids, const float* wts, void* stream) {
-  for (int ph = 0; ph < 3; ++ph)
+  for (int ph = 0; ph < 4; ++ph)
     if (zepp_layer_prepare_phase(l, ph, ids, wts, stream)) return 1;
   return 0;
 }
@@ -754,14 +810,15 @@ static int step_enqueue(zepp_layer* l, const int32_t* ids, const float* wts, con
   l->fuse_x = (!needs_loads(l) && l->c_max <= 1 && l->stage == nullptr) ? x : nullptr;
   l->x_fused = nullptr;
   if (zepp_layer_prepare_phase(l, 0, ids, wts, stream)) return 1;
+  if (zepp_layer_prepare_phase(l, 1, ids, wts, stream)) return 1;
   if (needs_loads(l) && l->stage == nullptr) {
     if (zepp_layer_forward_phase(l, 0, x, y, stream)) return 1;
-    if (zepp_layer_prepare_phase(l, 1, ids, wts, stream)) return 1;
+    if (zepp_layer_prepare_phase(l, 2, ids, wts, stream)) return 1;
   } else {
-    if (zepp_layer_prepare_phase(l, 1, ids, wts, stream)) return 1;     // commits the step counter
+    if (zepp_layer_prepare_phase(l, 2, ids, wts, stream)) return 1;     // commits the step counter
     if (zepp_layer_forward_phase(l, 0, x, y, stream)) return 1;
   }
-  if (zepp_layer_prepare_phase(l, 2, ids, wts, stream)) return 1;
+  if (zepp_layer_prepare_phase(l, 3, ids, wts, stream)) return 1;
   l->fuse_x = nullptr;
   for (int ph = 1; ph < 4; ++ph)
     if (zepp_layer_forward_phase(l, ph, x, y, stream)) return 1;

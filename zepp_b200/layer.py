@@ -110,8 +110,13 @@ class EPMoE(torch.nn.Module):
         and unassigned redundant slots stay zero."""
         cfg, shape = self.cfg, self.cfg.shape
         nlp, gpe = cfg.slots_per_rank, cfg.groups_per_rank
-        w1 = torch.zeros(gpe, shape.ffn1, shape.hidden, dtype=self.dtype, device=self.device)
-        w2 = torch.zeros(gpe, shape.hidden, shape.ffn_hidden, dtype=self.dtype, device=self.device)
+        if cfg.swap:       # swapped experts travel between ranks: the layer's own peer-visible slots
+            w1, w2 = self._h.weight_slots(gpe, shape.ffn1, shape.hidden, shape.ffn_hidden)
+            w1.zero_()
+            w2.zero_()
+        else:
+            w1 = torch.zeros(gpe, shape.ffn1, shape.hidden, dtype=self.dtype, device=self.device)
+            w2 = torch.zeros(gpe, shape.hidden, shape.ffn_hidden, dtype=self.dtype, device=self.device)
         for i in range(nlp):
             e = int(self.placement.p2l[self.rank * nlp + i])
             if e < 0:
@@ -126,6 +131,7 @@ class EPMoE(torch.nn.Module):
         assert w1_slots.shape == (gpe, shape.ffn1, shape.hidden), tuple(w1_slots.shape)
         assert w2_slots.shape == (gpe, shape.hidden, shape.ffn_hidden), tuple(w2_slots.shape)
         self.w1, self.w2 = w1_slots.contiguous(), w2_slots.contiguous()
+        torch.cuda.synchronize()
         self._h.set_weights(self.w1, self.w2)
 
     # -- setup ------------------------------------------------------------------------
@@ -150,7 +156,7 @@ class EPMoE(torch.nn.Module):
 
     def prepare(self, topk_ids, topk_weights, marks=None, phase=None):
         """Loads exchange -> (swap decision) -> route -> routing exchange -> metadata; returns the Plan.
-        `phase` (0, 1, 2) runs one stage only: ranks emulated inside one process advance in lock step.
+        `phase` (0..3) runs one stage only: ranks emulated inside one process advance in lock step.
         The id / weight tensors are read in place by the step's kernels (keep them unchanged until then)."""
         ids, wts = self._ids(topk_ids, topk_weights)
         self._keep = (ids, wts)
@@ -162,10 +168,11 @@ class EPMoE(torch.nn.Module):
             self._h.prepare(ids, wts, 1)
             marks("place")
             self._h.prepare(ids, wts, 2)
+            self._h.prepare(ids, wts, 3)
             marks("plan")
         else:
             self._h.prepare(ids, wts, phase)
-            if phase < 2:
+            if phase < 3:
                 return None
         self._epoch += 1
         if self._plan_views is None:          # runtime buffers: the addresses never change
@@ -242,7 +249,17 @@ class EPMoE(torch.nn.Module):
 
     @property
     def swap_moves(self):
-        return self._swap_moves
+        """Expert moves of the last step's swap decision (reads the device result block: synchronises)."""
+        if not self.cfg.swap:
+            return 0
+        return int(self._h.table("swap_block")[1])
+
+    def current_placement(self):
+        """The placement the device tables hold now (they change when a swap is decided)."""
+        from .placement import Placement, rebuild_l2p
+        p2l = self._h.table("p2l").cpu()
+        return Placement(p2l, rebuild_l2p(p2l, self.cfg.shape.num_experts, self.cfg.ranks), self.placement.lcnts,
+                         dict(self.placement.stats))
 
     def prep(self):
         """Per-iteration hygiene hook of the reference's benchmark loop: nothing to clear here (every
@@ -280,7 +297,7 @@ def make_local_layers(cfg: EPMoEConfig, sizing_routing, pool_routing, wait_limit
 
 def local_step(layers, ids_all, wts_all, xs):
     """One layer step of in-process ranks, phase by phase; returns the list of outputs."""
-    for ph in range(3):
+    for ph in range(4):
         for r, l in enumerate(layers):
             l.prepare(ids_all[r], wts_all[r], phase=ph)
     for ph in range(4):

@@ -110,6 +110,14 @@ class LayerHandle:
         assert w1.is_contiguous() and w2.is_contiguous()
         check(lib().zepp_layer_set_weights(self.h, ctypes.c_void_p(w1.data_ptr()), ctypes.c_void_p(w2.data_ptr())))
 
+    def weight_slots(self, gpe, ffn1, H, ffn):
+        """The layer-owned weight slots (swap on) as tensors w1 [gpe, ffn1, H], w2 [gpe, H, ffn]."""
+        p1, p2 = ctypes.c_void_p(), ctypes.c_void_p()
+        check(lib().zepp_layer_weight_slots(self.h, ctypes.byref(p1), ctypes.byref(p2)))
+        w1 = torch.as_tensor(_DevMem(p1.value, gpe * ffn1 * H, torch.bfloat16), device="cuda").view(torch.bfloat16)
+        w2 = torch.as_tensor(_DevMem(p2.value, gpe * H * ffn, torch.bfloat16), device="cuda").view(torch.bfloat16)
+        return w1.view(gpe, ffn1, H), w2.view(gpe, H, ffn)
+
     def prepare(self, ids, wts, phase=None):
         assert ids.is_cuda and ids.dtype == torch.int32 and ids.is_contiguous()
         assert wts.is_cuda and wts.dtype == torch.float32 and wts.is_contiguous()
