@@ -38,6 +38,7 @@ def parse():
     ap.add_argument("--strategy", default="overlap", choices=["overlap", "direct"])
     ap.add_argument("--tokens", type=int, default=0, help="tokens per rank (default: the workload's)")
     ap.add_argument("--cpu-baseline", type=int, default=1)
+    ap.add_argument("--swap", type=int, default=-1, help="expert swap on/off (default: the workload's setting)")
     return ap.parse_args()
 
 
@@ -171,9 +172,10 @@ def main():
         group = LocalGroup(0, 1)
 
     shape, S, ids, wts, _, _ = wl.make(args.workload, world, S=args.tokens or None)
-    _, _, _, router_c, _ = wl.WORKLOADS[args.workload]
+    _, _, _, router_c, wl_swap = wl.WORKLOADS[args.workload]
+    swap = bool(wl_swap if args.swap < 0 else args.swap) and args.strategy == "overlap" and world > 1
     cfg = EPMoEConfig(shape=shape, ranks=world, ranks_per_node=world, max_tokens_per_rank=S,
-                      comm_strategy=args.strategy, swap=False, router_c=router_c)
+                      comm_strategy=args.strategy, swap=swap, router_c=router_c)
     layer = EPMoE(cfg, group, sizing_routing=ids, pool_routing=ids)
     nlp = cfg.slots_per_rank
     hosted = [int(e) for e in layer.placement.p2l[rank * nlp:(rank + 1) * nlp].tolist() if e >= 0]
@@ -302,7 +304,7 @@ def main():
         "data": "synthetic",
         "config": {"workload": f"{args.workload}: H={H} I={I} E={shape.num_experts} top-{K} SwiGLU, {S} tokens/rank, "
                                f"{shape.num_experts // world} experts/rank, routing seed 0",
-                   "strategy": args.strategy, "parallelism": f"ep{world}", "router_c": router_c, "swap": 0,
+                   "strategy": args.strategy, "parallelism": f"ep{world}", "router_c": router_c, "swap": int(swap),
                    "l2": "expert weights streamed per step exceed the 126 MB L2 (inputs larger than L2)",
                    "timed": "prepare (device planning) + forward"},
         "latency_us": ms_step * 1e3,

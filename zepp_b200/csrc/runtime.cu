@@ -43,6 +43,7 @@ static int fail(const char* fmt, ...) {
     if (_e != cudaSuccess) return fail("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__, __LINE__); \
   } while (0)
 
+static int swap_decide_prepare();
 static size_t meta_smem(int R, int NN, int E_virt);
 static size_t pass2_smem(int tokens_per_tile, int K, int E_virt);
 static int pass2_prepare(size_t bytes);
@@ -439,6 +440,7 @@ extern "C" int zepp_layer_create(zepp_rt* rt, const zepp_layer_cfg* c, zepp_laye
   CU_OK(cudaFuncSetAttribute(moe_gemm_kernel<MODE_DOWN_COMBINE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              GemmCfg<MODE_DOWN_COMBINE>::kSmemBytes));
   if (pass2_prepare(pass2_smem(l->tokens_per_tile, l->K, l->E_virt))) { delete l; return 1; }
+  if (l->cfg.swap && swap_decide_prepare()) { delete l; return 1; }
   {
     const char* g = getenv("ZEPP_B200_GRAPHS");     // "0": launch the step's kernels one by one instead of as a graph
     if (g != nullptr && g[0] == '0') l->use_graphs = false;
@@ -597,10 +599,9 @@ extern "C" int zepp_layer_prepare_phase(zepp_layer* l, int phase, const int32_t*
       return 1;
     l->launches++;
     CU_OK(cudaMemsetAsync(l->sched, 0, l->gpe * 4, st));
-    if (zepp_lane_arm((const int64_t*)l->swap_block, R, me, l->nlp, 8, (int64_t*)l->gate, l->sched, (int64_t*)l->ovr0,
-                      (int64_t*)l->ovr1, (const int64_t*)l->stag, (int64_t)l->epoch, stream))
-      return 1;
-    l->launches++;
+    lane_arm_kernel<<<1, 32, 0, st>>>(l->swap_block, R, me, l->nlp, 8, l->gate, l->sched, l->ovr0, l->ovr1, l->stag, 0,
+                                      l->step_ctr);
+    LAUNCH_OK();
     SwapMoveArgs sm = layer_swap_args(l);
     swap_pull_kernel<<<l->rt->sm_count * 2, 256, 0, st>>>(sm);
     LAUNCH_OK();
@@ -828,12 +829,12 @@ static int step_enqueue(zepp_layer* l, const int32_t* ids, const float* wts, con
 // prepare + forward as one call.  The launch sequence of a step depends only on the four
 // pointers (every count, offset and the epoch live in device memory), so it is captured once
 // per pointer set into a CUDA graph and replayed: one graph launch per step instead of 6-9
-// kernel launches.  Graphs are skipped with swap on (the lane metadata bakes the host epoch).
+// kernel launches.
 extern "C" int zepp_layer_step(zepp_layer* l, const int32_t* ids, const float* wts, const void* x, void* y, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
   CU_OK(cudaSetDevice(l->rt->device));
   if (!l->have_weights) return fail("step: no weights set");
-  if (!l->use_graphs || l->cfg.swap) return step_enqueue(l, ids, wts, x, y, stream);
+  if (!l->use_graphs) return step_enqueue(l, ids, wts, x, y, stream);
   for (auto& gph : l->graphs) {
     if (gph.ids == ids && gph.wts == wts && gph.x == x && gph.y == y) {
       CU_OK(cudaGraphLaunch(gph.exec, st));
@@ -1054,6 +1055,15 @@ extern "C" int zepp_routed_meta(const int32_t* gathered, const int32_t* vce_in, 
   return 0;
 }
 
+static int swap_decide_prepare() {
+  static bool attr = false;
+  if (!attr) {
+    CU_OK(cudaFuncSetAttribute(swap_decide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    attr = true;
+  }
+  return 0;
+}
+
 extern "C" int zepp_swap_decide_out_ints(int R, int G, int nlp, int cap) { return 3 + R + 4 * R * cap + R * nlp + G; }
 
 extern "C" int zepp_swap_decide(const int32_t* loads, int32_t* p2l, int32_t* l2p, const int32_t* lcnts, int R, int G,
@@ -1066,11 +1076,7 @@ extern "C" int zepp_swap_decide(const int32_t* loads, int32_t* p2l, int32_t* l2p
   const int NS = R * nlp, NN = R / L, Q = NN * (L / 2) > 0 ? NN * (L / 2) : 1;
   const size_t sm = (size_t)(G + NS + R) * 8 + (size_t)(2 * NS + 7 * Q + NN + (kSwapThreads / 32) * 16 + 8) * 4;
   if (sm > 200 * 1024) return fail("swap_decide: tables too large for one block");
-  static bool attr = false;
-  if (!attr) {
-    CU_OK(cudaFuncSetAttribute(swap_decide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    attr = true;
-  }
+  if (swap_decide_prepare()) return 1;
   swap_decide_kernel<<<1, kSwapThreads, sm, st>>>(a);
   CU_OK(cudaGetLastError());
   return 0;
@@ -1080,7 +1086,7 @@ extern "C" int zepp_lane_arm(const int64_t* swap_out, int R, int rank, int nlp, 
                              int64_t* ovr0, int64_t* ovr1, const int64_t* stag, int64_t epoch, void* stream) {
   lane_arm_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((const long long*)swap_out, R, rank, nlp, cap, (long long*)gate,
                                                       sched, (long long*)ovr0, (long long*)ovr1,
-                                                      (const long long*)stag, (long long)epoch);
+                                                      (const long long*)stag, (long long)epoch, nullptr);
   CU_OK(cudaGetLastError());
   return 0;
 }

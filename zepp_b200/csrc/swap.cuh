@@ -262,8 +262,9 @@ __global__ void __launch_bounds__(kSwapThreads) swap_decide_kernel(SwapArgs a) {
 // staging addresses the GEMMs read incoming slots from.  A rank without incoming slots is untouched.
 __global__ void lane_arm_kernel(const long long* out, int R, int rank, int nlp, int cap, long long* gate,
                                 int* sched, long long* ovr0, long long* ovr1, const long long* stag,
-                                long long epoch) {
+                                long long epoch, const unsigned long long* epoch_ptr) {
   if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  if (epoch_ptr != nullptr) epoch = (long long)*epoch_ptr;      // the layer's device-resident step counter
   const int gpe = nlp + 1;
   const long long rounds = out[0];
   const int cnt = (int)out[3 + rank];
