@@ -24,6 +24,9 @@ import torch
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one dispatch-GEMM launch from the ncu capture summarised in
+# profiles/moe_gemm_qwen3-30b_1gpu.md, keyed by (workload, GPUs, tokens per rank)
+NCU_TRAFFIC = {("qwen3-30b", 1, 512): 851.1e6}
 METRIC = "moe_layer_tflops"
 UNIT = "TFLOP/s"
 
@@ -213,16 +216,36 @@ def main():
         plan = layer.prepare(ids_d, w_d, marks)
         return layer.forward(xs_dev[i % n_x], plan, marks)
 
-    ids_in = torch.empty_like(ids_d)
-    w_in = torch.empty_like(w_d)
-    x_in = torch.empty_like(xs_dev[0])
+    # end-to-end path: every step copies its inputs from pinned host memory and its output back.  Two
+    # buffer sets and two copy streams let the copies of neighbouring steps overlap the compute of this one
+    # (each step still waits for its own inputs and delivers its own output).
+    ids_in = [torch.empty_like(ids_d) for _ in range(2)]
+    w_in = [torch.empty_like(w_d) for _ in range(2)]
+    x_in = [torch.empty_like(xs_dev[0]) for _ in range(2)]
+    y_dev = [torch.empty_like(xs_dev[0]) for _ in range(2)]
+    y_pins = [y_pin, torch.empty_like(y_pin).pin_memory()]
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_done = [torch.cuda.Event() for _ in range(2)]
+    main = torch.cuda.current_stream()
+    for e in ev_done:
+        e.record(main)
 
     def step_e2e(i):
-        ids_in.copy_(ids_pin, non_blocking=True)
-        w_in.copy_(w_pin, non_blocking=True)
-        x_in.copy_(xs_host[i % n_x], non_blocking=True)
-        y = layer.step(ids_in, w_in, x_in)
-        y_pin.copy_(y, non_blocking=True)
+        b = i & 1
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(ev_done[b])               # step i-2 no longer reads this input set
+            ids_in[b].copy_(ids_pin, non_blocking=True)
+            w_in[b].copy_(w_pin, non_blocking=True)
+            x_in[b].copy_(xs_host[i % n_x], non_blocking=True)
+            ev_in[b].record(s_in)
+        main.wait_event(ev_in[b])
+        y = layer.step(ids_in[b], w_in[b], x_in[b])
+        y_dev[b].copy_(y, non_blocking=True)
+        ev_done[b].record(main)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_done[b])
+            y_pins[b].copy_(y_dev[b], non_blocking=True)
 
     # ---- device-resident steps (value) + per-kernel brackets (roofline)
     for i in range(args.warmup):
@@ -271,7 +294,8 @@ def main():
     t0.record()
     for i in range(args.steps):
         step_e2e(i)
-    t1.record()
+    s_out.wait_stream(main)
+    t1.record(s_out)                 # after the last output has landed in host memory
     barrier()
     ms_e2e = max_over_ranks(t0.elapsed_time(t1)) / args.steps
     layer.check()
@@ -317,11 +341,14 @@ def main():
                            "frac_of_3term": max(t_flop, t_hbm) / (ms_step * 1e-3), "rows_this_rank": m_r},
         "e2e": {"value": e2e_val, "unit": UNIT, "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": int(ids_pin.numel() * 4 + w_pin.numel() * 4 + xs_host[0].numel() * 2),
-                "d2h_bytes_per_step": int(y_pin.numel() * 2)},
+                "d2h_bytes_per_step": int(y_pin.numel() * 2),
+                "pipelined": "inputs of step i+1 and the output of step i-1 are copied on side streams during step i"},
         "gpu_launches": int(launches),
         "roofline": {"bound": "hbm", "kernel": "moe_gemm_kernel<gate|up + SwiGLU> (dispatch GEMM)", "achieved": achieved,
                      "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs, "peak_kind": peak_kind,
-                     "traffic": None, "algorithmic_bytes": alg_bytes, "kernel_ms": gemm1_ms},
+                     "traffic": NCU_TRAFFIC.get((args.workload, world, S)), "algorithmic_bytes": alg_bytes,
+                     "kernel_ms": gemm1_ms,
+                     "kernel_ms_device_stamps": (steady["gemm1_end"] - steady["gemm1"]) / 1e3 if steady.get("gemm1_end") else None},
         "clocks": clocks,
     }
     if rank == 0 and world == 1 and args.cpu_baseline:
