@@ -244,3 +244,29 @@ def test_swap_moves_weights_and_routes_on_the_new_placement():
             l.close()
         for rt in rts:
             rt.destroy()
+
+
+def test_full_size_benchmark_step_sampled_against_oracle():
+    """The benchmark's own configuration on one GPU (Qwen3-30B layer shape, all 128 experts, 512 tokens, top-8):
+    a graph-launched step, checked against the CPU oracle on a sample of tokens (the oracle needs seconds per
+    token batch at this size), plus exact conservation of the routed rows."""
+    shape = wl.shape_of("qwen3-30b")
+    S = 512
+    cfg = EPMoEConfig(shape=shape, ranks=1, ranks_per_node=1, max_tokens_per_rank=S)
+    _, _, ids, wts, _, _ = wl.make("qwen3-30b", 1)
+    layer = EPMoE(cfg, LocalGroup(0, 1), ids, ids)
+    wdev = wl.fast_weights(shape, range(shape.num_experts), torch.device("cuda"))
+    layer.load_weights(lambda e: wdev[e][0], lambda e: wdev[e][1])
+    x = wl.tokens(0, S, shape.hidden)
+    y = layer.step(ids[0].cuda(), wts[0].cuda(), x.cuda()).clone()
+    y_again = layer.step(ids[0].cuda(), wts[0].cuda(), x.cuda()).clone()
+    layer.check()
+    assert torch.equal(y, y_again)
+    splits, m_this = layer.tables("splits", "m_this")
+    assert int(splits.sum()) == S * shape.topk == int(m_this[0])
+    sample = torch.arange(0, S, 16)
+    W1 = torch.stack([wdev[e][0].cpu() for e in range(shape.num_experts)])
+    W2 = torch.stack([wdev[e][1].cpu() for e in range(shape.num_experts)])
+    ref = ol.moe_reference_fp32(x[sample], ids[0][sample], wts[0][sample], W1, W2)
+    _close(y[sample.cuda()], ref, "full-size sample")
+    layer.close()
