@@ -100,6 +100,12 @@ def test_single_rank_many_rows_per_expert(strategy):
 
 
 @pytest.mark.parametrize("strategy", ["direct", "overlap"])
+def test_hidden_with_an_odd_number_of_feature_blocks(strategy):
+    """hidden = 3 x 128: the combine GEMM's last item of an expert has only one of its two feature blocks."""
+    _run_local(ModelShape(16, 4, 384, 128, act="swiglu"), 2, 2, 200, strategy, zipf=1.0, steps=1)
+
+
+@pytest.mark.parametrize("strategy", ["direct", "overlap"])
 def test_single_rank_gelu(strategy):
     shape = ModelShape(16, 4, 256, 128, act="gelu")
     cfg = EPMoEConfig(shape=shape, ranks=1, ranks_per_node=1, max_tokens_per_rank=64, comm_strategy=strategy)

@@ -81,7 +81,10 @@ struct GemmArgs {
 
 template <int MODE>
 struct GemmCfg {
-  static constexpr bool kDual = (MODE == MODE_GATE_UP_SWIGLU);
+  // two weight tiles share one token tile per stage: gate | up rows of W1, or two neighbouring
+  // 128-feature blocks of W2 (halves the token-tile bytes each flop pulls out of L2 / HBM)
+  static constexpr bool kDual = (MODE == MODE_GATE_UP_SWIGLU || MODE == MODE_DOWN_COMBINE);
+  static constexpr int kFeatPerItem = (MODE == MODE_DOWN_COMBINE) ? 2 * kTileM : kTileM;   // output features of an item
   static constexpr int kStageBytes = (kDual ? 2 : 1) * kWTileBytes + kXTileBytes;
   static constexpr int kStages = kDual ? 4 : 6;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024;   // + alignment slack
@@ -204,7 +207,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         const CUtensorMap* tmx = rows <= 32 ? &tm_x32 : (rows <= 64 ? &tm_x64 : &tm_x128);
         const uint32_t x_bytes = (rows <= 32 ? 32u : (rows <= 64 ? 64u : 128u)) * (kTileK * 2);
         const uint32_t tx = (Cfg::kDual ? 2u : 1u) * kWTileBytes + x_bytes;
-        const int w_row = grp * a.w_rows_per_group + j * kTileM;
+        const int w_row = grp * a.w_rows_per_group + j * Cfg::kFeatPerItem;
         int kb_first = 0;
         if (MODE != MODE_DOWN_COMBINE && a.gather) {
           // rows of this tile are pulled by gather warps (of any CTA).  If they have not all landed yet,
@@ -347,52 +350,67 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
       tc_fence_after();
       const uint32_t t0 = tmem_base + acc * Cfg::kAccCols + ((uint32_t)(quad * 32) << 16);
       const int fcol = quad * 32 + lane;        // feature inside the 128-feature tile
+      constexpr int kHalves = (MODE == MODE_DOWN_COMBINE) ? 2 : 1;   // 128-feature blocks written per item
+      const int feat0 = j * Cfg::kFeatPerItem;
       for (int c0 = 0; c0 < rows; c0 += 32) {
-        uint32_t g[32];
-        __nv_bfloat16 (*stg)[kTileM] = s_stage[buf];
-        tmem_ld_32x32(t0 + c0, g);
-        if (MODE == MODE_GATE_UP_SWIGLU) {
-          uint32_t u[32];
-          tmem_ld_32x32(t0 + kTileN + c0, u);
-          tmem_ld_wait();
-#pragma unroll
-          for (int n = 0; n < 32; ++n) stg[n][fcol] = swiglu_bf16(__uint_as_float(g[n]), __uint_as_float(u[n]));
-        } else if (MODE == MODE_SINGLE_GELU) {
-          tmem_ld_wait();
-#pragma unroll
-          for (int n = 0; n < 32; ++n) stg[n][fcol] = gelu_bf16(__uint_as_float(g[n]));
-        } else {
-          tmem_ld_wait();
-          // lane n holds the top-k weight of row c0 + n; broadcast per column.  Reference rounding
-          // points (combine_kernels.cu:191-197): bf16 GEMM output, fp32 product, bf16 row on the wire
-          float my_scale = 0.f;
-          if (c0 + lane < rows) my_scale = a.row_scale[row0 + c0 + lane];
-#pragma unroll
-          for (int n = 0; n < 32; ++n) {
-            const float sc = __shfl_sync(0xffffffffu, my_scale, n);
-            stg[n][fcol] = __float2bfloat16_rn(bf16_round(__uint_as_float(g[n])) * sc);
-          }
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        // write-out: warp ew owns rows ew*8 .. ew*8+7 of the chunk, two rows per instruction
+        // destination of the rows this thread writes (the same for both feature blocks of the item)
+        __nv_bfloat16* outp[4];
 #pragma unroll
         for (int rr = 0; rr < 4; ++rr) {
           const int r = ew * 8 + rr * 2 + (lane >> 4);
+          outp[rr] = nullptr;
           if (c0 + r < rows) {
-            const uint4 v = *reinterpret_cast<const uint4*>(&stg[r][(lane & 15) * 8]);
-            __nv_bfloat16* out;
             if (MODE != MODE_DOWN_COMBINE) {
-              out = a.act + (size_t)(row0 + c0 + r) * a.ld_act;
+              outp[rr] = a.act + (size_t)(row0 + c0 + r) * a.ld_act;
             } else if (a.staging != nullptr) {
-              out = a.staging + (size_t)(row0 + c0 + r) * a.w_rows_per_group;
+              outp[rr] = a.staging + (size_t)(row0 + c0 + r) * a.w_rows_per_group;
             } else {
               const long long dst = a.row_dst[row0 + c0 + r];
-              out = dst >= 0 ? a.panels[(int)(dst >> 40)] + (size_t)(dst & ((1ll << 40) - 1)) : nullptr;
+              outp[rr] = dst >= 0 ? a.panels[(int)(dst >> 40)] + (size_t)(dst & ((1ll << 40) - 1)) : nullptr;
             }
-            if (out != nullptr) *reinterpret_cast<uint4*>(out + j * kTileM + (lane & 15) * 8) = v;
           }
         }
-        buf ^= 1;       // the next chunk stages into the other buffer; its barrier orders the reuse
+        float my_scale = 0.f;
+        if (MODE == MODE_DOWN_COMBINE && c0 + lane < rows) my_scale = a.row_scale[row0 + c0 + lane];
+#pragma unroll
+        for (int h = 0; h < kHalves; ++h) {
+          // an odd number of 128-feature blocks: the last item's second block lies past the expert's rows
+          if (MODE == MODE_DOWN_COMBINE && feat0 + h * kTileM >= a.w_rows_per_group) break;
+          uint32_t g[32];
+          __nv_bfloat16 (*stg)[kTileM] = s_stage[buf];
+          tmem_ld_32x32(t0 + h * kTileN + c0, g);
+          if (MODE == MODE_GATE_UP_SWIGLU) {
+            uint32_t u[32];
+            tmem_ld_32x32(t0 + kTileN + c0, u);
+            tmem_ld_wait();
+#pragma unroll
+            for (int n = 0; n < 32; ++n) stg[n][fcol] = swiglu_bf16(__uint_as_float(g[n]), __uint_as_float(u[n]));
+          } else if (MODE == MODE_SINGLE_GELU) {
+            tmem_ld_wait();
+#pragma unroll
+            for (int n = 0; n < 32; ++n) stg[n][fcol] = gelu_bf16(__uint_as_float(g[n]));
+          } else {
+            tmem_ld_wait();
+            // lane n holds the top-k weight of row c0 + n; broadcast per column.  Reference rounding
+            // points (combine_kernels.cu:191-197): bf16 GEMM output, fp32 product, bf16 row on the wire
+#pragma unroll
+            for (int n = 0; n < 32; ++n) {
+              const float sc = __shfl_sync(0xffffffffu, my_scale, n);
+              stg[n][fcol] = __float2bfloat16_rn(bf16_round(__uint_as_float(g[n])) * sc);
+            }
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          // write-out: warp ew owns rows ew*8 .. ew*8+7 of the chunk, two rows per instruction
+#pragma unroll
+          for (int rr = 0; rr < 4; ++rr) {
+            const int r = ew * 8 + rr * 2 + (lane >> 4);
+            if (outp[rr] != nullptr) {
+              const uint4 v = *reinterpret_cast<const uint4*>(&stg[r][(lane & 15) * 8]);
+              *reinterpret_cast<uint4*>(outp[rr] + feat0 + h * kTileM + (lane & 15) * 8) = v;
+            }
+          }
+          buf ^= 1;     // the next chunk stages into the other buffer; its barrier orders the reuse
+        }
       }
       tc_fence_before();
       __syncwarp();

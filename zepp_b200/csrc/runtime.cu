@@ -682,9 +682,11 @@ static GemmArgs layer_gemm_args(zepp_layer* l, bool first) {
   GemmArgs g{};
   g.tt.n_tiles = l->n_tiles; g.tt.tile_group = l->tile_group; g.tt.tile_row0 = l->tile_row0; g.tt.tile_rows = l->tile_rows;
   g.k_extent = first ? l->H : l->I;
-  g.n_feat_tiles = first ? l->I / kTileM : l->H / kTileM;
+  // dispatch GEMM: one 128-feature block of gate and of up per item (or of W1 alone without a gate);
+  // combine GEMM: two neighbouring 128-feature blocks of W2 per item
+  g.n_feat_tiles = first ? l->I / kTileM : (l->H + 2 * kTileM - 1) / (2 * kTileM);
   g.w_rows_per_group = first ? l->ffn1 : l->H;
-  g.up_row_offset = l->I;
+  g.up_row_offset = first ? l->I : kTileM;
   g.act = l->act; g.ld_act = l->I;
   g.row_scale = l->row_scale; g.row_dst = l->row_dst; g.panels = l->panels; g.staging = nullptr;
   g.done_flags = nullptr; g.cta_counter = l->counters + 2;
