@@ -141,6 +141,13 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// one 32-byte store (a whole sector): sm_100 has 256-bit global stores; the address is 32-byte aligned
+__device__ __forceinline__ void st_global_v8(void* p, const uint32_t (&w)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+               "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+               : "memory");
+}
+
 // ---------------------------------------------------------------------------------------
 // TMA (tiled 2D loads, no multicast anywhere in this library)
 // ---------------------------------------------------------------------------------------

@@ -1,38 +1,50 @@
 // Grouped expert GEMMs of the MoE layer on tcgen05 / TMEM (sm_100a).
 //
-// Both GEMMs run "weights on the M side": the 128 rows of an MMA tile are 128 output features
-// (rows of an expert's weight matrix, K-major as stored), the N side is a tile of up to 128 routed
-// token rows of that expert (also K-major), so tiny per-expert row counts (decode, 32 rows per
-// expert at 512 tokens per rank) still use full-height MMA tiles and the kernel streams each weight
-// panel exactly once per token tile.  D[feature, token] accumulates in TMEM in fp32.
+// A tile of up to 128 routed token rows of one expert is the M side of the MMA (TMEM lanes), the
+// expert's weight rows are the N side: one M128 x N256 x K16 instruction per K step covers the gate
+// and the up block of W1 (dispatch GEMM) or two neighbouring 128-feature blocks of W2 (combine
+// GEMM).  Both operands are K-major as stored.  D[token, feature] accumulates in TMEM in fp32, two
+// accumulator stages of 256 columns, so the epilogue of one item runs under the MMAs of the next.
+// With few rows per expert (decode: 32 rows at 512 tokens per rank) the kernel is bound by streaming
+// each weight panel once from HBM and the unused MMA rows cost nothing; with many rows it is bound
+// by shared-memory bandwidth (operand reads of the MMAs + TMA fills), which is why one N = 256
+// instruction replaces two N = 128 ones that would each re-read the token tile.
 //
 //   dispatch GEMM  (replaces src/dispatch/cutlass_impls/ag_scatter_gemm_grouped_with_absmax.h:420-731
-//                   + python/zepp/layer.py:20-27): gate and up tiles of W1 share one token tile and
-//                   accumulate into two TMEM regions; the epilogue applies SwiGLU and writes bf16
-//                   activations [row, I].
+//                   + python/zepp/layer.py:20-27): the epilogue applies SwiGLU to the gate / up
+//                   columns of a token and writes bf16 activations [row, I].
 //   combine GEMM   (replaces src/combine/cutlass_impls/gather_rs_gemm_grouped_with_absmax.h and
-//                   src/combine/combine_kernels.cu:106-304): W2 tile x activation tile; the epilogue
-//                   multiplies by the copy's top-k weight and stores the bf16 row slice straight into
-//                   the home rank's [S, K, H] slot panel (a peer-mapped pointer over NVLink).
+//                   src/combine/combine_kernels.cu:106-304): the epilogue multiplies a token's row by
+//                   the copy's top-k weight and stores the bf16 row slice straight into the home
+//                   rank's [S, K, H] slot panel (a peer-mapped pointer over NVLink).
 //
 // One persistent CTA per SM, 6 warps: warp 0 = TMA producer, warp 1 = MMA issuer (owns TMEM),
-// warps 2..5 = epilogue (one TMEM lane quadrant each).  Optional warps 6..9 (dispatch GEMM, fused
-// mode) pull routed token rows from the source ranks' symmetric x buffers into the local receive
-// buffer, tile by tile in schedule order, and publish per-tile ready counters that the producer
-// waits on before it issues the tile's TMA loads.
+// warps 2..5 = epilogue (one TMEM lane quadrant = 32 token rows each; a thread owns one token and
+// writes contiguous pieces of its row).  Optional warps 6.. (dispatch GEMM, fused mode) assemble the
+// routed token rows in the local receive buffer, tile by tile in schedule order, and publish
+// per-tile ready counters that the producer waits on before it issues the tile's TMA loads.
 #pragma once
 #include "common.cuh"
 
 namespace zepp {
 
-constexpr int kTileM = 128;       // output features per MMA tile (TMEM lanes)
-constexpr int kTileN = 128;       // max token rows per tile (TMEM columns per accumulator)
+constexpr int kTileM = 128;       // output features per weight block (128 TMEM columns)
+constexpr int kTileN = 128;       // token rows per tile (TMEM lanes)
 constexpr int kTileK = 64;        // bf16 elements per smem row = 128 bytes = one swizzle row
 constexpr int kWTileBytes = kTileM * kTileK * 2;   // 16 KB
 constexpr int kXTileBytes = kTileN * kTileK * 2;   // 16 KB
 constexpr int kAccStages = 2;
 constexpr int kMaxGatherWarps = 8;     // warps 6.. of a dispatch GEMM CTA in fused mode (4 or 8, chosen at launch)
 constexpr int kMaxTilesSmem = 1024;   // token tiles of one rank and step held in shared memory
+
+// -DZEPP_GEMM_PROFILE: CTA 0 of the dispatch GEMM sums, in SM cycles, how long its MMA thread waited for
+// operand stages (status word 26) and for a free accumulator (27), and how long an epilogue warp worked
+// (28) and waited for accumulators (29).  Off in the shipped library.
+#ifdef ZEPP_GEMM_PROFILE
+#define ZEPP_PROF(...) __VA_ARGS__
+#else
+#define ZEPP_PROF(...)
+#endif
 
 enum GemmMode : int { MODE_GATE_UP_SWIGLU = 0, MODE_SINGLE_GELU = 1, MODE_DOWN_COMBINE = 2 };
 
@@ -100,7 +112,7 @@ __device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(_
 __device__ __forceinline__ __nv_bfloat16 swiglu_bf16(float gate_acc, float up_acc) {
   const float g = bf16_round(gate_acc);
   const float u = bf16_round(up_acc);
-  const float s = bf16_round(g / (1.0f + __expf(-g)));
+  const float s = bf16_round(__fdividef(g, 1.0f + __expf(-g)));   // 2-ulp fp32 quotient, then rounded to bf16
   return __float2bfloat16_rn(s * u);
 }
 __device__ __forceinline__ __nv_bfloat16 gelu_bf16(float acc) {
@@ -125,8 +137,6 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
   __shared__ uint32_t tmem_base_smem;
   __shared__ int abort_flag;
   __shared__ int s_row0[kMaxTilesSmem], s_gr[kMaxTilesSmem];      // first row; (group << 9) | rows
-  __shared__ __align__(16) __nv_bfloat16 s_stage[2][32][kTileM];   // epilogue transpose buffers
-  __shared__ int s_epi_ok;
   __shared__ int s_pref[kMaxTilesSmem + 1];                        // rows before tile i in schedule order
 
   const int warp = threadIdx.x >> 5;
@@ -277,37 +287,37 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
+      // tokens x (two weight blocks): one instruction per K step, whatever the tile's valid rows (rows
+      // of the token tile beyond them hold stale shared memory and only reach accumulator rows that
+      // the epilogue never reads)
+      const uint32_t idesc = make_idesc_bf16_m128(Cfg::kDual ? 2u * kTileM : (uint32_t)kTileM);
+      ZEPP_PROF(long long prof_data = 0; long long prof_acc = 0; long long prof_t;)
       for (int item = item_first; item < total_items && !*abortp; item += item_stride) {
-        const int ti = item / a.n_feat_tiles;
-        const int rows = s_gr[ti] & 0x1FF;
-        const uint32_t n_mma = (uint32_t)((rows + 15) & ~15);
-        const uint32_t idesc = make_idesc_bf16_m128(n_mma);
+        ZEPP_PROF(prof_t = clock64();)
         if (!mbar_wait_bounded(&acc_empty_bar[acc], acc_phase ^ 1, abortp, a.mbar_limit)) {
           record_timeout(a.status, WAIT_TMEM_EMPTY, item, acc);
           abort_flag = 1;
           break;
         }
+        ZEPP_PROF(prof_acc += clock64() - prof_t;)
         tc_fence_after();
         const uint32_t d0 = tmem_base + acc * Cfg::kAccCols;
         bool ok = true;
         for (int kb = 0; kb < k_blocks; ++kb) {
+          ZEPP_PROF(prof_t = clock64();)
           if (!mbar_wait_bounded(&full_bar[stage], phase, abortp, a.mbar_limit)) {
             record_timeout(a.status, WAIT_MBAR_FULL, item, kb);
             abort_flag = 1;
             ok = false;
             break;
           }
+          ZEPP_PROF(prof_data += clock64() - prof_t;)
           tc_fence_after();
           const uint32_t st = smem_u32(smem + stage * Cfg::kStageBytes);
-          const uint64_t w0 = make_kmajor_sw128_desc(st);
-          const uint64_t w1 = make_kmajor_sw128_desc(st + kWTileBytes);
+          const uint64_t wd = make_kmajor_sw128_desc(st);     // 128 or 256 weight rows (the blocks are adjacent)
           const uint64_t xd = make_kmajor_sw128_desc(st + (Cfg::kDual ? 2 : 1) * kWTileBytes);
 #pragma unroll
-          for (int k = 0; k < kTileK / 16; ++k) {
-            const uint32_t accum = (kb | k) != 0 ? 1u : 0u;
-            umma_bf16(d0, w0 + 2 * k, xd + 2 * k, idesc, accum);
-            if (Cfg::kDual) umma_bf16(d0 + kTileN, w1 + 2 * k, xd + 2 * k, idesc, accum);
-          }
+          for (int k = 0; k < kTileK / 16; ++k) umma_bf16(d0, xd + 2 * k, wd + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
           umma_commit(&empty_bar[stage]);       // stage reusable once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -315,108 +325,136 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         umma_commit(&acc_full_bar[acc]);        // accumulator complete
         if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
       }
+      ZEPP_PROF(if (blockIdx.x == 0 && a.status != nullptr && MODE != MODE_DOWN_COMBINE) {
+        a.status[26] = (unsigned long long)prof_data; a.status[27] = (unsigned long long)prof_acc; })
     }
     __syncwarp();
   } else if (warp < 6) {
     // ------------------------------------------------------------------ epilogue (4 warps)
-    // TMEM holds D[feature, token]; a thread owns one feature (lane of its quadrant) and reads 32
-    // tokens at a time.  The 32 x 128 chunk is transposed through shared memory so that global
-    // stores are 16-byte vectors covering 256 contiguous bytes of a token row (full lines for the
-    // local activation buffer and for the home rank's panel across NVLink).
+    // TMEM holds D[token, feature]: a thread owns one token row of the tile (the lane of its warp's
+    // quadrant), reads 32 feature columns at a time and writes them as contiguous 16-byte vectors of
+    // that token's output row.  Nothing is staged in shared memory and the warps never synchronise
+    // with each other.
     const int quad = warp & 3;                  // TMEM lane quadrant this warp may read
-    const int ew = warp - 2;                    // 0..3 among the epilogue warps
+    const int tok = quad * 32 + lane;           // token row inside the tile
     int acc = 0;
     uint32_t acc_phase = 0;
-    int buf = 0;
+    ZEPP_PROF(long long prof_busy = 0; long long prof_wait = 0; long long prof_t = clock64();)
     for (int item = item_first; item < total_items; item += item_stride) {
       const int ti = item / a.n_feat_tiles;
       const int j = item - ti * a.n_feat_tiles;
       const int row0 = s_row0[ti];
       const int rows = s_gr[ti] & 0x1FF;
-      // one warp waits for the accumulator and tells the others, so all four take the same branch
-      if (ew == 0) {
-        int got = 0;
-        if (lane == 0) {
-          got = mbar_wait_bounded(&acc_full_bar[acc], acc_phase, abortp, a.mbar_limit) ? 1 : 0;
-          if (!got && !*abortp) {
-            record_timeout(a.status, WAIT_TMEM_FULL, item, acc);
-            abort_flag = 1;
+      const bool mine = tok < rows;
+      // where this token's row goes (and its top-k weight): looked up while the item's MMAs still run
+      __nv_bfloat16* out = nullptr;
+      float scale = 0.f;
+      if (mine) {
+        if (MODE != MODE_DOWN_COMBINE) {
+          out = a.act + (size_t)(row0 + tok) * a.ld_act + j * kTileM;
+        } else {
+          scale = a.row_scale[row0 + tok];
+          if (a.staging != nullptr) {
+            out = a.staging + (size_t)(row0 + tok) * a.w_rows_per_group;
+          } else {
+            const long long dst = a.row_dst[row0 + tok];
+            if (dst >= 0) out = a.panels[(int)(dst >> 40)] + (size_t)(dst & ((1ll << 40) - 1));
           }
-          s_epi_ok = got;
+          if (out != nullptr) out += j * Cfg::kFeatPerItem;
         }
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (!s_epi_ok) break;
-      tc_fence_after();
-      const uint32_t t0 = tmem_base + acc * Cfg::kAccCols + ((uint32_t)(quad * 32) << 16);
-      const int fcol = quad * 32 + lane;        // feature inside the 128-feature tile
-      constexpr int kHalves = (MODE == MODE_DOWN_COMBINE) ? 2 : 1;   // 128-feature blocks written per item
-      const int feat0 = j * Cfg::kFeatPerItem;
-      for (int c0 = 0; c0 < rows; c0 += 32) {
-        // destination of the rows this thread writes (the same for both feature blocks of the item)
-        __nv_bfloat16* outp[4];
-#pragma unroll
-        for (int rr = 0; rr < 4; ++rr) {
-          const int r = ew * 8 + rr * 2 + (lane >> 4);
-          outp[rr] = nullptr;
-          if (c0 + r < rows) {
-            if (MODE != MODE_DOWN_COMBINE) {
-              outp[rr] = a.act + (size_t)(row0 + c0 + r) * a.ld_act;
-            } else if (a.staging != nullptr) {
-              outp[rr] = a.staging + (size_t)(row0 + c0 + r) * a.w_rows_per_group;
-            } else {
-              const long long dst = a.row_dst[row0 + c0 + r];
-              outp[rr] = dst >= 0 ? a.panels[(int)(dst >> 40)] + (size_t)(dst & ((1ll << 40) - 1)) : nullptr;
-            }
-          }
+      int got = 1;
+      if (lane == 0) {
+        got = mbar_wait_bounded(&acc_full_bar[acc], acc_phase, abortp, a.mbar_limit) ? 1 : 0;
+        if (!got && !*abortp) {
+          record_timeout(a.status, WAIT_TMEM_FULL, item, acc);
+          abort_flag = 1;
         }
-        float my_scale = 0.f;
-        if (MODE == MODE_DOWN_COMBINE && c0 + lane < rows) my_scale = a.row_scale[row0 + c0 + lane];
-#pragma unroll
-        for (int h = 0; h < kHalves; ++h) {
-          // an odd number of 128-feature blocks: the last item's second block lies past the expert's rows
-          if (MODE == MODE_DOWN_COMBINE && feat0 + h * kTileM >= a.w_rows_per_group) break;
-          uint32_t g[32];
-          __nv_bfloat16 (*stg)[kTileM] = s_stage[buf];
-          tmem_ld_32x32(t0 + h * kTileN + c0, g);
-          if (MODE == MODE_GATE_UP_SWIGLU) {
-            uint32_t u[32];
-            tmem_ld_32x32(t0 + kTileN + c0, u);
+      }
+      got = __shfl_sync(0xffffffffu, got, 0);
+      if (!got) break;
+      ZEPP_PROF(prof_wait += clock64() - prof_t; prof_t = clock64();)
+      tc_fence_after();
+      if (quad * 32 < rows) {                   // warps whose 32 token rows are all padding skip the reads
+        const uint32_t t0 = tmem_base + acc * Cfg::kAccCols + ((uint32_t)(quad * 32) << 16);
+        if (MODE == MODE_GATE_UP_SWIGLU) {
+          for (int c0 = 0; c0 < kTileM; c0 += 32) {
+            uint32_t g[32], u[32];
+            tmem_ld_32x32(t0 + c0, g);
+            tmem_ld_32x32(t0 + kTileM + c0, u);
             tmem_ld_wait();
+            if (out != nullptr) {
 #pragma unroll
-            for (int n = 0; n < 32; ++n) stg[n][fcol] = swiglu_bf16(__uint_as_float(g[n]), __uint_as_float(u[n]));
-          } else if (MODE == MODE_SINGLE_GELU) {
-            tmem_ld_wait();
+              for (int q = 0; q < 2; ++q) {
+                uint32_t w[8];
 #pragma unroll
-            for (int n = 0; n < 32; ++n) stg[n][fcol] = gelu_bf16(__uint_as_float(g[n]));
-          } else {
-            tmem_ld_wait();
-            // lane n holds the top-k weight of row c0 + n; broadcast per column.  Reference rounding
-            // points (combine_kernels.cu:191-197): bf16 GEMM output, fp32 product, bf16 row on the wire
-#pragma unroll
-            for (int n = 0; n < 32; ++n) {
-              const float sc = __shfl_sync(0xffffffffu, my_scale, n);
-              stg[n][fcol] = __float2bfloat16_rn(bf16_round(__uint_as_float(g[n])) * sc);
+                for (int e = 0; e < 8; ++e) {
+                  const int n = q * 16 + e * 2;
+                  const __nv_bfloat162 p = __halves2bfloat162(
+                      swiglu_bf16(__uint_as_float(g[n]), __uint_as_float(u[n])),
+                      swiglu_bf16(__uint_as_float(g[n + 1]), __uint_as_float(u[n + 1])));
+                  w[e] = *reinterpret_cast<const uint32_t*>(&p);
+                }
+                st_global_v8(out + c0 + q * 16, w);
+              }
             }
           }
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          // write-out: warp ew owns rows ew*8 .. ew*8+7 of the chunk, two rows per instruction
+        } else if (MODE == MODE_SINGLE_GELU) {
+          for (int c0 = 0; c0 < kTileM; c0 += 32) {
+            uint32_t g[32];
+            tmem_ld_32x32(t0 + c0, g);
+            tmem_ld_wait();
+            if (out != nullptr) {
 #pragma unroll
-          for (int rr = 0; rr < 4; ++rr) {
-            const int r = ew * 8 + rr * 2 + (lane >> 4);
-            if (outp[rr] != nullptr) {
-              const uint4 v = *reinterpret_cast<const uint4*>(&stg[r][(lane & 15) * 8]);
-              *reinterpret_cast<uint4*>(outp[rr] + feat0 + h * kTileM + (lane & 15) * 8) = v;
+              for (int q = 0; q < 2; ++q) {
+                uint32_t w[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  const int n = q * 16 + e * 2;
+                  const __nv_bfloat162 p = __halves2bfloat162(gelu_bf16(__uint_as_float(g[n])),
+                                                              gelu_bf16(__uint_as_float(g[n + 1])));
+                  w[e] = *reinterpret_cast<const uint32_t*>(&p);
+                }
+                st_global_v8(out + c0 + q * 16, w);
+              }
             }
           }
-          buf ^= 1;     // the next chunk stages into the other buffer; its barrier orders the reuse
+        } else {
+          // reference rounding points (combine_kernels.cu:191-197): bf16 GEMM output, fp32 product with
+          // the top-k weight, bf16 row on the wire.  64 features = 128 contiguous bytes per step.
+          // An odd number of 128-feature blocks: the last item's second block lies past the expert's rows.
+          const int feat_end = min(Cfg::kFeatPerItem, a.w_rows_per_group - j * Cfg::kFeatPerItem);
+          for (int c0 = 0; c0 < feat_end; c0 += 64) {
+            uint32_t g[32], h[32];
+            tmem_ld_32x32(t0 + c0, g);
+            tmem_ld_32x32(t0 + c0 + 32, h);
+            tmem_ld_wait();
+            if (out != nullptr) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint32_t w[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  const int n = (q & 1) * 16 + e * 2;
+                  const float v0 = __uint_as_float(q < 2 ? g[n] : h[n]);
+                  const float v1 = __uint_as_float(q < 2 ? g[n + 1] : h[n + 1]);
+                  const __nv_bfloat162 p = __floats2bfloat162_rn(bf16_round(v0) * scale, bf16_round(v1) * scale);
+                  w[e] = *reinterpret_cast<const uint32_t*>(&p);
+                }
+                st_global_v8(out + c0 + q * 16, w);
+              }
+            }
+          }
         }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
       if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
+      ZEPP_PROF(prof_busy += clock64() - prof_t; prof_t = clock64();)
     }
+    ZEPP_PROF(if (blockIdx.x == 0 && warp == 2 && lane == 0 && a.status != nullptr && MODE != MODE_DOWN_COMBINE) {
+      a.status[28] = (unsigned long long)prof_busy; a.status[29] = (unsigned long long)prof_wait; })
   } else {
     // ------------------------------------------------------------------ gather warps (fused dispatch)
     if (MODE != MODE_DOWN_COMBINE && a.gather) {
