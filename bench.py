@@ -41,6 +41,9 @@ def parse():
     ap.add_argument("--strategy", default="overlap", choices=["overlap", "direct"])
     ap.add_argument("--tokens", type=int, default=0, help="tokens per rank (default: the workload's)")
     ap.add_argument("--cpu-baseline", type=int, default=1)
+    ap.add_argument("--trace-dir", default="", help="trace replay: draw the routing from this trace directory "
+                    "(manifest.json + <model>/eval.txt, pool.txt) with the reference's batch sampler")
+    ap.add_argument("--budget-mib", type=float, default=4.0, help="trace replay: send budget per rank (sets tokens/rank)")
     ap.add_argument("--swap", type=int, default=-1, help="expert swap on/off (default: the workload's setting)")
     return ap.parse_args()
 
@@ -174,12 +177,16 @@ def main():
     else:
         group = LocalGroup(0, 1)
 
-    shape, S, ids, wts, _, _ = wl.make(args.workload, world, S=args.tokens or None)
+    if args.trace_dir:
+        shape, S, ids, wts, pool_ids, trace_model = wl.from_trace(args.workload, world, args.trace_dir, args.budget_mib)
+    else:
+        shape, S, ids, wts, _, _ = wl.make(args.workload, world, S=args.tokens or None)
+        pool_ids, trace_model = ids, None
     _, _, _, router_c, wl_swap = wl.WORKLOADS[args.workload]
     swap = bool(wl_swap if args.swap < 0 else args.swap) and args.strategy == "overlap" and world > 1
     cfg = EPMoEConfig(shape=shape, ranks=world, ranks_per_node=world, max_tokens_per_rank=S,
                       comm_strategy=args.strategy, swap=swap, router_c=router_c)
-    layer = EPMoE(cfg, group, sizing_routing=ids, pool_routing=ids)
+    layer = EPMoE(cfg, group, sizing_routing=ids, pool_routing=pool_ids)
     nlp = cfg.slots_per_rank
     hosted = [int(e) for e in layer.placement.p2l[rank * nlp:(rank + 1) * nlp].tolist() if e >= 0]
     wts_dev = wl.fast_weights(shape, hosted, dev)
@@ -325,9 +332,11 @@ def main():
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic",
+        "data": "synthetic" if not trace_model else f"routing replayed from trace slice '{trace_model}' "
+                                                        f"({args.budget_mib} MiB budget); tokens and weights synthetic",
         "config": {"workload": f"{args.workload}: H={H} I={I} E={shape.num_experts} top-{K} SwiGLU, {S} tokens/rank, "
-                               f"{shape.num_experts // world} experts/rank, routing seed 0",
+                               f"{shape.num_experts // world} experts/rank, "
+                               + ("routing seed 0" if not trace_model else "trace-replay routing"),
                    "strategy": args.strategy, "parallelism": f"ep{world}", "router_c": router_c, "swap": int(swap),
                    "l2": "expert weights streamed per step exceed the 126 MB L2 (inputs larger than L2)",
                    "timed": "prepare (device planning) + forward"},

@@ -276,3 +276,45 @@ def test_full_size_benchmark_step_sampled_against_oracle():
     ref = ol.moe_reference_fp32(x[sample], ids[0][sample], wts[0][sample], W1, W2)
     _close(y[sample.cuda()], ref, "full-size sample")
     layer.close()
+
+
+def test_trace_replay_batch_through_the_layer():
+    """Routing drawn by the reference's batch sampler from a trace slice (here the committed synthetic slice),
+    pool window for the placement: two emulated ranks, layer output and routed metadata against the oracle."""
+    import os
+    from zepp_b200 import traces
+    data = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "traces")
+    ts = traces.load_slice("qwen3", data)
+    shape = ModelShape(ts.num_experts, ts.topk, 256, 128, act="swiglu")
+    W, chunk, budget = 2, 256 * 2, 64 * 512 / (1 << 20)
+    S = traces.tokens_per_rank(budget, chunk, ts.topk)
+    assert S == 64
+    ids = torch.tensor(traces.sample_batch(ts, W, W, budget, chunk), dtype=torch.int32).view(W, S, ts.topk)
+    pool = torch.tensor(traces.pool_routing(ts, W, 256), dtype=torch.int32)
+    gen = torch.Generator().manual_seed(5)
+    wts = torch.softmax(torch.randn(W, S, ts.topk, generator=gen), dim=-1)
+    cfg = EPMoEConfig(shape=shape, ranks=W, ranks_per_node=W, max_tokens_per_rank=S)
+    layers, rts = make_local_layers(cfg, ids, pool, wait_limit_ms=500)
+    W1, W2 = _weights(shape)
+    try:
+        for l in layers:
+            l.load_weights(lambda e: W1[e], lambda e: W2[e])
+        xs = [wl.tokens(r, S, shape.hidden, seed=3) for r in range(W)]
+        ys = local_step(layers, [ids[r].cuda() for r in range(W)], [wts[r].cuda() for r in range(W)], [x.cuda() for x in xs])
+        for l in layers:
+            l.check()
+        refs = _reference(xs, ids, wts, W1, W2)
+        for r in range(W):
+            _close(ys[r], refs[r], f"trace replay rank{r}")
+        pl0 = layers[0].placement
+        pl = op.Placement(pl0.p2l.numpy(), pl0.l2p.numpy(), pl0.lcnts.numpy())
+        phys, _ = op.reference_route(ids.numpy(), pl, cfg.slots_per_rank, W, cfg.router_c)
+        vce = op.virtual_route(phys.reshape(W * S, -1), cfg.slots_per_rank, cfg.groups_per_rank)
+        splits, scat, _, _ = op.routed_meta(vce, W, S, cfg.groups_per_rank, 1, W)
+        assert np.array_equal(layers[1].tables("splits")[0].cpu().numpy(), splits)
+        assert np.array_equal(layers[1].tables("scatter_index")[0].cpu().numpy().reshape(scat.shape), scat)
+    finally:
+        for l in layers:
+            l.close()
+        for rt in rts:
+            rt.destroy()

@@ -85,3 +85,23 @@ def make(name, W, seed=0, S=None):
     p = popularity(shape.num_experts, zipf_s, gen)
     ids, wts = routing(W, S, shape.topk, p, gen)
     return shape, S, ids, wts, p, gen
+
+
+def from_trace(name, W, data_dir, budget_mib, seed=0):
+    """A named workload's shape with routing drawn from a trace directory (zepp_b200/traces.py) instead of
+    the synthetic popularity: (shape, S, ids [W,S,K], wts [W,S,K], pool ids [W,S,K], trace model key).
+    The batch is the reference sampler's batch for (slice, W ranks on one node, budget, row bytes);
+    gate weights are seeded softmax (traces hold expert ids only)."""
+    from . import traces
+    shape = shape_of(name)
+    model = {128: "qwen3", 384: "k2"}[shape.num_experts]
+    ts = traces.load_slice(model, data_dir)
+    assert ts.topk == shape.topk and ts.num_experts == shape.num_experts, (ts.topk, ts.num_experts)
+    chunk = shape.hidden * 2                                   # one bf16 token row
+    S = traces.tokens_per_rank(budget_mib, chunk, ts.topk)
+    rows = traces.sample_batch(ts, W, W, budget_mib, chunk)
+    ids = torch.tensor(rows, dtype=torch.int32).view(W, S, shape.topk)
+    gen = torch.Generator().manual_seed(seed)
+    wts = torch.softmax(torch.randn(W, S, shape.topk, generator=gen), dim=-1)
+    pool = torch.tensor(traces.pool_routing(ts, W, S), dtype=torch.int32)
+    return shape, S, ids, wts, pool, model
