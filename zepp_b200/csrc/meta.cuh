@@ -28,6 +28,17 @@ struct MetaArgs {
   const int* gathered;
   const int* gathered_odd;  // odd-epoch copy when `epoch_ptr` is set
   const int* vce_in;
+  // one rank with a single-replica placement: the routing is a slot lookup and is done here, the step's
+  // first kernel (no routing launch, no exchange); local_topk = nullptr otherwise
+  const int* local_topk;    // [SK] expert ids of this rank's tokens
+  const float* local_probs; // [SK]
+  const int* slot_of;       // [G] the only physical slot of every expert (-1: none)
+  int G;
+  int* phys_own;            // [SK] out
+  int* send_row;            // [2*SK] out: phys | weight bits
+  int* gathered_out;        // [2*SK] out: the same row in the gather table of this epoch's parity
+  int* gathered_out_odd;
+  unsigned long long* ctr;  // step counter committed by the last block
   int R, L, S, K, nlp, gpe, my_rank;
   int tokens_per_tile, tiles_per_src;
   // outputs
@@ -78,9 +89,16 @@ __global__ void __launch_bounds__(kMetaThreads) meta_pass1_kernel(MetaArgs a) {
   const int R = a.R, NN = a.R / a.L, E_virt = a.R * a.gpe, SK = a.S * a.K;
   int* hist = sm;                       // [E_virt]
   int* ucs = sm + E_virt;               // [R + NN]
-  const unsigned long long epoch = step_epoch(a.epoch_ptr, false);
-  if (a.epoch_ptr != nullptr && (epoch & 1)) a.gathered = a.gathered_odd;
-  if (blockIdx.x == 0 && threadIdx.x == 0) trace_mark(a.status, TR_PASS1);
+  const bool local = a.local_topk != nullptr;
+  const unsigned long long epoch = step_epoch(a.epoch_ptr, local);
+  if (a.epoch_ptr != nullptr && (epoch & 1)) { a.gathered = a.gathered_odd; a.gathered_out = a.gathered_out_odd; }
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    if (local) {
+      trace_mark(a.status, TR_ROUTE);
+      trace_mark(a.status, TR_RING + (int)(epoch & 15));
+    }
+    trace_mark(a.status, TR_PASS1);
+  }
   if (!block_wait_all(a.routing_flags, R, epoch, a.limit_ns, a.status, WAIT_ROUTING)) return;
   if (blockIdx.x == 0 && threadIdx.x == 0) trace_mark(a.status, TR_PASS1_GO);
   const int src = blockIdx.x / a.tiles_per_src;
@@ -93,7 +111,22 @@ __global__ void __launch_bounds__(kMetaThreads) meta_pass1_kernel(MetaArgs a) {
   for (int n = n_lo + threadIdx.x; n < n_hi; n += blockDim.x) {
     int v;
     const size_t flat = (size_t)src * SK + n;
-    if (a.gathered) {
+    if (local) {
+      const int e = a.local_topk[n];
+      int phys = 0;
+      if (e < 0 || e >= a.G) {
+        if (a.status) atomicOr(a.status + ST_ERROR, (unsigned long long)ERR_BAD_INDEX);
+      } else if ((phys = a.slot_of[e]) < 0) {
+        if (a.status) atomicOr(a.status + ST_ERROR, (unsigned long long)ERR_ROUTE);
+        phys = 0;
+      }
+      const float w = a.local_probs[n];
+      a.phys_own[n] = phys;
+      a.send_row[n] = phys; a.send_row[SK + n] = __float_as_int(w);
+      a.gathered_out[n] = phys; a.gathered_out[SK + n] = __float_as_int(w);
+      a.probs_all[flat] = w;
+      v = (phys / a.nlp) * a.gpe + 1 + phys % a.nlp;
+    } else if (a.gathered) {
       const int phys = a.gathered[(size_t)src * 2 * SK + n];
       v = (phys / a.nlp) * a.gpe + 1 + phys % a.nlp;
       a.probs_all[flat] = __int_as_float(a.gathered[(size_t)src * 2 * SK + SK + n]);
@@ -135,6 +168,8 @@ __global__ void __launch_bounds__(kMetaThreads) meta_pass1_kernel(MetaArgs a) {
   if (!is_last) return;
   __threadfence();
   meta_scan_body(a, sm);
+  // every block has read the counter by now (they all arrived before this block was chosen)
+  if (local && threadIdx.x == 0 && a.ctr != nullptr) *a.ctr = epoch;
 }
 
 // Exact demands of a step (python/zepp/capacity.py:30-55) from chunks[s][d] (rows from source s to

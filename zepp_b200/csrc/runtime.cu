@@ -509,6 +509,11 @@ extern "C" int zepp_layer_set_weights(zepp_layer* l, const void* w1, const void*
     l->launches++;                                                                           \
   } while (0)
 
+static bool needs_loads(const zepp_layer* l);
+// One rank, one replica per expert, nobody consuming the loads: the routing is a slot lookup that the
+// first metadata kernel does itself (no routing launch).
+static bool local_route(const zepp_layer* l) { return l->W == 1 && l->c_max <= 1 && !needs_loads(l) && !l->cfg.swap; }
+
 static MetaArgs layer_meta_args(zepp_layer* l) {
   MetaArgs m{};
   m.gathered = l->xchg_all[0];
@@ -530,6 +535,11 @@ static MetaArgs layer_meta_args(zepp_layer* l) {
   m.routing_flags = l->W > 1 ? l->routing_flags : nullptr;
   m.epoch_ptr = l->step_ctr; m.limit_ns = l->rt->wait_ns; m.status = l->status;
   m.block_counter = l->counters + 8;
+  if (local_route(l)) {
+    m.local_topk = l->ids_in; m.local_probs = l->wts_in; m.slot_of = l->slot_of; m.G = l->G;
+    m.phys_own = l->phys_own; m.send_row = l->send_row;
+    m.gathered_out = l->xchg_all[0]; m.gathered_out_odd = l->xchg_all[1]; m.ctr = l->step_ctr;
+  }
   return m;
 }
 
@@ -616,6 +626,7 @@ extern "C" int zepp_layer_prepare_phase(zepp_layer* l, int phase, const int32_t*
       slot_table_kernel<<<(l->G + 127) / 128, 128, 0, st>>>(l->l2p, l->lcnts, l->G, l->W, l->slot_of);
       LAUNCH_OK();
     }
+    if (local_route(l)) return 0;        // done by the first metadata kernel
     if (l->c_max <= 1) {
       SimpleRouteArgs sa{};
       sa.topk_own = l->ids_in; sa.probs_own = l->wts_in; sa.slot_of = l->slot_of;
