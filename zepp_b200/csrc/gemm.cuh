@@ -120,7 +120,13 @@ __device__ __forceinline__ __nv_bfloat16 gelu_bf16(float acc) {
   return __float2bfloat16_rn(0.5f * h * (1.0f + erff(h * 0.70710678118654752f)));
 }
 
-template <int MODE>
+// LINES (combine GEMM only): the epilogue writes whole 128-byte lines of the destination rows instead
+// of 32-byte pieces.  Each epilogue warp stages its 32 token rows x 64 features in its own 4 KB of
+// shared memory (16-byte units XOR-swizzled by the row, so neither the row-wise writes nor the
+// line-wise reads conflict) and eight lanes then store one row's 128 contiguous bytes.  Meant for
+// destination panels on peer GPUs, where NVLink carries a few large writes far better than many
+// 32-byte ones.
+template <int MODE, bool LINES = false>
 __global__ void __launch_bounds__(192 + 32 * kMaxGatherWarps, 1)
 moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x32,
                 const __grid_constant__ CUtensorMap tm_x64, const __grid_constant__ CUtensorMap tm_x128,
@@ -138,6 +144,8 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
   __shared__ int abort_flag;
   __shared__ int s_row0[kMaxTilesSmem], s_gr[kMaxTilesSmem];      // first row; (group << 9) | rows
   __shared__ int s_pref[kMaxTilesSmem + 1];                        // rows before tile i in schedule order
+  static_assert(!LINES || MODE == MODE_DOWN_COMBINE, "line staging belongs to the combine epilogue");
+  __shared__ uint4 s_lines[LINES ? 4 : 1][LINES ? 256 : 1];        // per epilogue warp: 32 rows x 8 units of 16 bytes
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -429,7 +437,33 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             tmem_ld_32x32(t0 + c0, g);
             tmem_ld_32x32(t0 + c0 + 32, h);
             tmem_ld_wait();
-            if (out != nullptr) {
+            if (LINES) {
+              uint4* stg = s_lines[warp - 2];
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {           // this row's 64 features as eight 16-byte units
+                uint32_t w[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const int n = (q & 3) * 8 + e * 2;
+                  const float v0 = __uint_as_float(q < 4 ? g[n] : h[n]);
+                  const float v1 = __uint_as_float(q < 4 ? g[n + 1] : h[n + 1]);
+                  const __nv_bfloat162 p = __floats2bfloat162_rn(bf16_round(v0) * scale, bf16_round(v1) * scale);
+                  w[e] = *reinterpret_cast<const uint32_t*>(&p);
+                }
+                stg[lane * 8 + (q ^ (lane & 7))] = make_uint4(w[0], w[1], w[2], w[3]);
+              }
+              __syncwarp();
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {           // four rows per instruction, eight lanes per row
+                const int r = 4 * i + (lane >> 3);
+                const int q = lane & 7;
+                const uint4 v = stg[r * 8 + (q ^ (r & 7))];
+                __nv_bfloat16* po = reinterpret_cast<__nv_bfloat16*>(
+                    __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(out), r));
+                if (po != nullptr) *reinterpret_cast<uint4*>(po + c0 + q * 8) = v;
+              }
+              __syncwarp();                           // the next 64 features reuse the staging
+            } else if (out != nullptr) {
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
                 uint32_t w[8];

@@ -246,6 +246,7 @@ struct zepp_layer {
   unsigned long long* step_ctr = nullptr;     // device-resident step counter (epoch of the running step)
   int c_max = 1;                              // largest replica count of the resident placement
   bool use_graphs = true;
+  bool combine_lines = false;                 // combine epilogue writes staged 128-byte lines (ZEPP_B200_COMBINE_STAGED=1)
   const void* fuse_x = nullptr;       // x of a whole-step call, published by the routing kernel
   const void* x_fused = nullptr;
   cudaStream_t capture_stream = nullptr;
@@ -439,11 +440,17 @@ extern "C" int zepp_layer_create(zepp_rt* rt, const zepp_layer_cfg* c, zepp_laye
                              GemmCfg<MODE_SINGLE_GELU>::kSmemBytes));
   CU_OK(cudaFuncSetAttribute(moe_gemm_kernel<MODE_DOWN_COMBINE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              GemmCfg<MODE_DOWN_COMBINE>::kSmemBytes));
+  CU_OK(cudaFuncSetAttribute(moe_gemm_kernel<MODE_DOWN_COMBINE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             GemmCfg<MODE_DOWN_COMBINE>::kSmemBytes));
   if (pass2_prepare(pass2_smem(l->tokens_per_tile, l->K, l->E_virt))) { delete l; return 1; }
   if (l->cfg.swap && swap_decide_prepare()) { delete l; return 1; }
   {
     const char* g = getenv("ZEPP_B200_GRAPHS");     // "0": launch the step's kernels one by one instead of as a graph
     if (g != nullptr && g[0] == '0') l->use_graphs = false;
+    // "1": the combine GEMM's epilogue stages rows in shared memory and stores whole 128-byte lines (for panels
+    // on peer GPUs).  Off unless asked for: this variant has not had its parity run on a GPU yet.
+    const char* cs = getenv("ZEPP_B200_COMBINE_STAGED");
+    if (cs != nullptr && cs[0] == '1') l->combine_lines = true;
   }
   if (meta_smem(l->W, l->NN, l->E_virt) > 48 * 1024) { delete l; return fail("too many ranks / experts for the metadata kernels"); }
   *out = l;
@@ -713,7 +720,7 @@ static GemmArgs layer_gemm_args(zepp_layer* l, bool first) {
   return g;
 }
 
-template <int MODE>
+template <int MODE, bool LINES = false>
 static int launch_gemm(zepp_layer* l, const CUtensorMap& tw, const CUtensorMap* tx, GemmArgs& g, cudaStream_t st) {
   // more gather warps when most rows cross NVLink (latency-bound pulls), fewer when they are local
   const int threads = g.gather ? 192 + 32 * (l->W >= 4 ? kMaxGatherWarps : 4) : 192;
@@ -722,11 +729,11 @@ static int launch_gemm(zepp_layer* l, const CUtensorMap& tw, const CUtensorMap* 
   if (g.gather) {
     // gather warps of one CTA feed the producers of others: every CTA must be resident
     void* args[] = {(void*)&tw, (void*)&tx[0], (void*)&tx[1], (void*)&tx[2], (void*)&g};
-    CU_OK(cudaLaunchCooperativeKernel((const void*)moe_gemm_kernel<MODE>, dim3(grid), dim3(threads), args, smem, st));
+    CU_OK(cudaLaunchCooperativeKernel((const void*)moe_gemm_kernel<MODE, LINES>, dim3(grid), dim3(threads), args, smem, st));
     l->launches++;
     return 0;
   }
-  moe_gemm_kernel<MODE><<<grid, threads, smem, st>>>(tw, tx[0], tx[1], tx[2], g);
+  moe_gemm_kernel<MODE, LINES><<<grid, threads, smem, st>>>(tw, tx[0], tx[1], tx[2], g);
   LAUNCH_OK();
   return 0;
 }
@@ -794,7 +801,11 @@ extern "C" int zepp_layer_forward_phase(zepp_layer* l, int phase, const void* x,
     } else if (l->W > 1) {
       g.done_flags = l->done_ptrs;
     }
-    if (launch_gemm<MODE_DOWN_COMBINE>(l, l->tm_w2, l->tm_act, g, st)) return 1;
+    if (l->combine_lines) {
+      if (launch_gemm<MODE_DOWN_COMBINE, true>(l, l->tm_w2, l->tm_act, g, st)) return 1;
+    } else {
+      if (launch_gemm<MODE_DOWN_COMBINE>(l, l->tm_w2, l->tm_act, g, st)) return 1;
+    }
     if (direct) {
       MoveArgs m = layer_move_args(l);
       combine_push_kernel<<<l->rt->sm_count * 2, 256, 0, st>>>(m);
