@@ -109,7 +109,7 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(self.sm)}
 
 
-def cpu_reference_sample(shape, ids, wts, seed, iters, tokens=128):
+def cpu_reference_sample(shape, ids, wts, seed, iters, tokens=128, warmup=2):
     """The reference's fp32 SwiGLU layer (oracle/layer.py) on the first `tokens` tokens of rank 0, all host
     threads.  Returns (TFLOP/s, seconds per pass, threads)."""
     from oracle import layer as ol
@@ -123,7 +123,7 @@ def cpu_reference_sample(shape, ids, wts, seed, iters, tokens=128):
     W2 = 0.02 * torch.randn(E, shape.hidden, shape.ffn_hidden, generator=g)
     x = wl.tokens(0, ids.shape[1], shape.hidden, seed=seed, dtype=torch.float32)[:T]
     i0, w0 = ids[0, :T], wts[0, :T]
-    for _ in range(2):
+    for _ in range(warmup):
         ol.moe_reference_fp32(x, i0, w0, W1, W2)
     ts = []
     for _ in range(iters):
@@ -141,9 +141,7 @@ def run_reference(args, rank):
         return
     from zepp_b200 import workloads as wl
     shape, S, ids, wts, _, _ = wl.make(args.workload, max(args.gpus, 1), S=args.tokens or None)
-    for _ in range(max(args.warmup - 2, 0)):
-        pass
-    tf, sec, threads, T = cpu_reference_sample(shape, ids, wts, 0, max(args.steps, 3))
+    tf, sec, threads, T = cpu_reference_sample(shape, ids, wts, 0, max(args.steps, 3), warmup=min(max(args.warmup, 1), 5))
     line = {"impl": "reference", "metric": METRIC, "value": tf, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
