@@ -22,6 +22,13 @@ enum StatusWord : int {
   // device timeline of the last step (globaltimer ns), written by block 0 / the last block of each kernel
   TR_ROUTE = 8, TR_PASS1 = 9, TR_PASS1_GO = 10, TR_PASS2 = 11, TR_GEMM1 = 12, TR_GEMM1_X = 13, TR_GEMM1_END = 14,
   TR_GEMM2 = 15, TR_GEMM2_END = 16, TR_REDUCE = 17, TR_REDUCE_GO = 18, TR_REDUCE_END = 19,
+  // inside the scan block of the first metadata kernel
+  TR_SCAN = 20, TR_SCAN_COUNTS = 21, TR_SCAN_BASES = 22, TR_SCAN_DEMANDS = 23, TR_SCAN_SCHED = 24, TR_SCAN_END = 25,
+  // cycle sums of a -DZEPP_GEMM_PROFILE build (not time stamps): MMA thread waiting for operand stages / for a free
+  // accumulator, epilogue warp working / waiting
+  TR_PROF_MMA_DATA = 26, TR_PROF_MMA_ACC = 27, TR_PROF_EPI_BUSY = 28, TR_PROF_EPI_WAIT = 29,
+  TR_GATHER_END = 30,  // dispatch GEMM: the last gather warp finished (max over warps)
+  TR_FIRST_ITEMS = 31, // dispatch GEMM: latest start of a CTA's first item (max over CTAs)
   TR_RING = 32,        // start stamps of the last 16 steps (slot = epoch % 16), then their end stamps
   ST_WORDS = 64
 };

@@ -38,8 +38,8 @@ constexpr int kMaxGatherWarps = 8;     // warps 6.. of a dispatch GEMM CTA in fu
 constexpr int kMaxTilesSmem = 1024;   // token tiles of one rank and step held in shared memory
 
 // -DZEPP_GEMM_PROFILE: CTA 0 of the dispatch GEMM sums, in SM cycles, how long its MMA thread waited for
-// operand stages (status word 26) and for a free accumulator (27), and how long an epilogue warp worked
-// (28) and waited for accumulators (29).  Off in the shipped library.
+// operand stages and for a free accumulator, and how long an epilogue warp worked and waited for
+// accumulators (status words TR_PROF_*).  Off in the shipped library.
 #ifdef ZEPP_GEMM_PROFILE
 #define ZEPP_PROF(...) __VA_ARGS__
 #else
@@ -270,7 +270,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
           } else {
             fence_proxy_async();
           }
-          if (item == item_first) trace_mark_max(a.status, 31);     // latest first-item start over the CTAs
+          if (item == item_first) trace_mark_max(a.status, TR_FIRST_ITEMS);
         }
         for (int kb = kb_first; kb < k_blocks; ++kb) {
           if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abortp, a.mbar_limit)) {
@@ -334,7 +334,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
       }
       ZEPP_PROF(if (blockIdx.x == 0 && a.status != nullptr && MODE != MODE_DOWN_COMBINE) {
-        a.status[26] = (unsigned long long)prof_data; a.status[27] = (unsigned long long)prof_acc; })
+        a.status[TR_PROF_MMA_DATA] = (unsigned long long)prof_data; a.status[TR_PROF_MMA_ACC] = (unsigned long long)prof_acc; })
     }
     __syncwarp();
   } else if (warp < 6) {
@@ -488,7 +488,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
       ZEPP_PROF(prof_busy += clock64() - prof_t; prof_t = clock64();)
     }
     ZEPP_PROF(if (blockIdx.x == 0 && warp == 2 && lane == 0 && a.status != nullptr && MODE != MODE_DOWN_COMBINE) {
-      a.status[28] = (unsigned long long)prof_busy; a.status[29] = (unsigned long long)prof_wait; })
+      a.status[TR_PROF_EPI_BUSY] = (unsigned long long)prof_busy; a.status[TR_PROF_EPI_WAIT] = (unsigned long long)prof_wait; })
   } else {
     // ------------------------------------------------------------------ gather warps (fused dispatch)
     if (MODE != MODE_DOWN_COMBINE && a.gather) {
@@ -587,7 +587,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             }
           }
         }
-        if (lane == 0) trace_mark_max(a.status, 30);                 // gather finished (latest warp)
+        if (lane == 0) trace_mark_max(a.status, TR_GATHER_END);
       }
     }
   }

@@ -280,7 +280,7 @@ __device__ void meta_scan_body(MetaArgs& a, int* sm) {
   __shared__ int warp_tot[33];
   __shared__ long long viol;
   __syncthreads();
-  if (threadIdx.x == 0) trace_mark(a.status, 20);
+  if (threadIdx.x == 0) trace_mark(a.status, TR_SCAN);
   for (int i = threadIdx.x; i < R * R; i += blockDim.x) chunks[i] = 0;
   __syncthreads();
   // per source splits, totals, chunk table
@@ -305,7 +305,7 @@ __device__ void meta_scan_body(MetaArgs& a, int* sm) {
     s_uc[i] = acc;
   }
   __syncthreads();
-  if (threadIdx.x == 0) trace_mark(a.status, 21);
+  if (threadIdx.x == 0) trace_mark(a.status, TR_SCAN_COUNTS);
   // exclusive scan of splits -> expert_base (E_virt <= 4 * blockDim)
   {
     const int per = (E_virt + blockDim.x - 1) / blockDim.x;
@@ -320,7 +320,7 @@ __device__ void meta_scan_body(MetaArgs& a, int* sm) {
     if (threadIdx.x == 0) { a.expert_base[E_virt] = total; s_base[E_virt] = total; }
   }
   __syncthreads();
-  if (threadIdx.x == 0) trace_mark(a.status, 22);
+  if (threadIdx.x == 0) trace_mark(a.status, TR_SCAN_BASES);
   for (int e = threadIdx.x; e < E_virt; e += blockDim.x) {      // tile histograms -> tile bases, in place
     int run = s_base[e];
     for (int b = 0; b < n_blocks; ++b) {
@@ -330,7 +330,7 @@ __device__ void meta_scan_body(MetaArgs& a, int* sm) {
     }
   }
   if (threadIdx.x == 0) {
-    trace_mark(a.status, 23);
+    trace_mark(a.status, TR_SCAN_DEMANDS);
     long long out[8];
     demands_from_chunks(chunks, s_uc, R, a.L, a.relay_slots, a.direct, a.caps, out);
     for (int i = 0; i < 8; ++i) a.demands[i] = out[i];
@@ -341,7 +341,7 @@ __device__ void meta_scan_body(MetaArgs& a, int* sm) {
     }
   }
   __syncthreads();
-  if (threadIdx.x == 0) trace_mark(a.status, 24);
+  if (threadIdx.x == 0) trace_mark(a.status, TR_SCAN_SCHED);
   // ---- this rank's GEMM schedule: token tiles of its groups in row order, one thread per group;
   //      groups marked as moved-in (bit 30 of their schedule word) go last (their weights land late)
   if (a.n_tiles != nullptr) {
@@ -371,7 +371,7 @@ __device__ void meta_scan_body(MetaArgs& a, int* sm) {
       }
     }
     if (threadIdx.x == 0) {
-      trace_mark(a.status, 25);
+      trace_mark(a.status, TR_SCAN_END);
       a.m_this[0] = m_this;
       a.m_this[1] = m_start;
       *a.n_tiles = min(tot_early + tot_late, a.max_tiles);

@@ -222,13 +222,13 @@ class EPMoE(torch.nn.Module):
 
     TRACE_NAMES = ("route", "pass1", "pass1_go", "pass2", "gemm1", "gemm1_x", "gemm1_end", "gemm2", "gemm2_end",
                    "reduce", "reduce_go", "reduce_end", "scan", "scan_counts", "scan_bases", "scan_demands",
-                   "scan_sched", "scan_end", "dplan_end", "cplan_end", "dplan_start", "dplan_mid", "gather_end", "first_items")
+                   "scan_sched", "scan_end", None, None, None, None, "gather_end", "first_items")   # None: profile-build counters
 
     def trace(self):
         """Device timeline of the last step: microseconds of each stamp after the step's first kernel."""
         t = self._h.trace()[8:8 + len(self.TRACE_NAMES)]
         t0 = t[0]
-        return {n: (v - t0) / 1e3 if v else None for n, v in zip(self.TRACE_NAMES, t)}
+        return {n: (v - t0) / 1e3 if v else None for n, v in zip(self.TRACE_NAMES, t) if n is not None}
 
     def step_ring(self):
         """(start, end) device stamps in microseconds of the last 16 steps, oldest first, relative to the oldest start."""
