@@ -59,9 +59,9 @@ struct TileTables {
 struct GemmArgs {
   TileTables tt;
   int k_extent;            // H (dispatch GEMM) or I (combine GEMM)
-  int n_feat_tiles;        // feature tiles per expert: I/128 or H/128
+  int n_feat_tiles;        // items per token tile: I/128 (dispatch GEMM) or ceil(H/256) (combine GEMM)
   int w_rows_per_group;    // rows of one expert's weight matrix: 2I, I or H
-  int up_row_offset;       // I for gate|up, unused otherwise
+  int up_row_offset;       // weight rows between an item's two blocks: I (gate -> up) or 128 (next block of W2)
   // dispatch GEMM output
   __nv_bfloat16* act;      // [cap, ld_act]
   int ld_act;
