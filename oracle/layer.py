@@ -10,8 +10,11 @@ the token's output row.  It is also the CPU baseline that bench.py times.
 product, bf16 down projection, fp32 weighted sum, one final rounding.
 
 The reference holds no golden vectors for layer outputs (its checks are tolerance checks against
-these torch paths), so the layer oracle is pinned to the reference only by restating those two
-functions; the planner oracle beside it is pinned bit for bit by golden vectors.
+these torch paths).  Both functions are pinned to outputs of the reference's own check code on small
+seeded inputs: tests/golden/layer_cases.npz, made by tests/golden/make_layer_golden.py, which runs
+examples/serving_check.py `reference` as it is and the bf16 loop of bench/replay.py around the
+reference's `zepp.layer.activation` (tests/test_oracle_layer_golden.py).  The planner oracle beside it
+is pinned bit for bit by golden vectors.
 """
 import torch
 
@@ -40,9 +43,10 @@ def moe_reference_fp32(x, ids, w, W1, W2):
 
 
 @torch.no_grad()
-def moe_reference_bf16_points(x, ids, w, W1, W2):
+def moe_reference_bf16_points(x, ids, w, W1, W2, act="swiglu"):
     """Same layer with the bf16 rounding points of the reference's bf16 check path; inputs bf16
-    tensors (W1/W2 may be given as dicts or tensors indexed by expert)."""
+    tensors (W1/W2 may be given as dicts or tensors indexed by expert).  act="gelu": W1 is [*, I, H] and the
+    activation is the exact (erf) GELU on the bf16 projection (python/zepp/layer.py:22-23)."""
     n, K = ids.shape
     H = x.shape[1]
     y = torch.zeros(n, H, dtype=torch.float32)
@@ -51,10 +55,13 @@ def moe_reference_bf16_points(x, ids, w, W1, W2):
     for e in torch.unique(ids).tolist():
         rows, ks = (ids == e).nonzero(as_tuple=True)
         w1, w2 = W1[e].float(), W2[e].float()
-        ffn = w1.shape[0] // 2
         h = (x[rows].float() @ w1.t()).to(bf)
-        g = torch.nn.functional.silu(h[:, :ffn].float()).to(bf)
-        a = (g.float() * h[:, ffn:].float()).to(bf)
+        if act == "gelu":
+            a = torch.nn.functional.gelu(h.float()).to(bf)
+        else:
+            ffn = w1.shape[0] // 2
+            g = torch.nn.functional.silu(h[:, :ffn].float()).to(bf)
+            a = (g.float() * h[:, ffn:].float()).to(bf)
         part = (a.float() @ w2.t()).to(bf)
         y.index_add_(0, rows, part.float() * w[rows, ks].float().unsqueeze(1))
     return y.to(bf)
