@@ -213,7 +213,7 @@ struct zepp_layer {
   __nv_bfloat16* panel;              // [S*K, H]
   // local buffers
   __nv_bfloat16 *recv, *act, *staging;
-  int *slot_of, *topk_own, *phys_own, *send_row, *route_ws, *p2l, *l2p, *lcnts, *p2l_try, *l2p_try;
+  int *slot_of, *topk_own, *phys_own, *send_row, *route_ws, *p2l, *l2p, *lcnts;
   float* probs_own;
   long long* route_stats;
   int *vce, *splits, *scatter_index, *sps, *uc, *tile_hist, *tile_uc, *expert_base;
@@ -318,9 +318,7 @@ static int layer_alloc(zepp_layer* l) {
   LA(l->route_ws, zepp_route_workspace_ints(l->G, R));
   LA(l->route_stats, 4);
   LA(l->p2l, R * l->nlp);
-  LA(l->p2l_try, R * l->nlp);
   LA(l->l2p, l->G * R);
-  LA(l->l2p_try, l->G * R);
   LA(l->lcnts, l->G);
   LA(l->slot_of, l->G);
   LA(l->vce, (size_t)R * l->SK);
