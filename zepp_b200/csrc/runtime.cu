@@ -250,6 +250,10 @@ struct zepp_layer {
   const void* fuse_x = nullptr;       // x of a whole-step call, published by the routing kernel
   const void* x_fused = nullptr;
   cudaStream_t capture_stream = nullptr;
+  // ZEPP_B200_PUSH_FORK=1: the dispatch push runs on a branch of the step beside the metadata kernels
+  bool push_fork = false;
+  cudaStream_t push_stream = nullptr;
+  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
   struct StepGraph {
     const void *ids, *wts, *x, *y;
     cudaGraphExec_t exec;
@@ -447,6 +451,16 @@ extern "C" int zepp_layer_create(zepp_rt* rt, const zepp_layer_cfg* c, zepp_laye
     if (g != nullptr && g[0] == '0') l->use_graphs = false;
     // "1": the combine GEMM's epilogue stages rows in shared memory and stores whole 128-byte lines (for panels
     // on peer GPUs).  Off unless asked for: this variant has not had its parity run on a GPU yet.
+    // "1": the staged dispatch push leaves the step's main line after the routing kernel and rejoins it before the
+    // reduce, so it overlaps the metadata kernels and the start of the dispatch GEMM.  Off unless asked for: an
+    // earlier form of it slowed the metadata kernels on the small shape and it has not been re-measured.
+    const char* pf = getenv("ZEPP_B200_PUSH_FORK");
+    if (pf != nullptr && pf[0] == '1' && l->stage != nullptr) {
+      CU_OK(cudaStreamCreateWithFlags(&l->push_stream, cudaStreamNonBlocking));
+      CU_OK(cudaEventCreateWithFlags(&l->ev_fork, cudaEventDisableTiming));
+      CU_OK(cudaEventCreateWithFlags(&l->ev_join, cudaEventDisableTiming));
+      l->push_fork = true;
+    }
     const char* cs = getenv("ZEPP_B200_COMBINE_STAGED");
     if (cs != nullptr && cs[0] == '1') l->combine_lines = true;
   }
@@ -461,6 +475,9 @@ extern "C" int zepp_layer_destroy(zepp_layer* l) {
     cudaDeviceSynchronize();
     for (auto& gph : l->graphs) cudaGraphExecDestroy(gph.exec);
     if (l->capture_stream) cudaStreamDestroy(l->capture_stream);
+    if (l->push_stream) cudaStreamDestroy(l->push_stream);
+    if (l->ev_fork) cudaEventDestroy(l->ev_fork);
+    if (l->ev_join) cudaEventDestroy(l->ev_join);
     delete l;
   }
   return 0;
@@ -839,12 +856,23 @@ static int step_enqueue(zepp_layer* l, const int32_t* ids, const float* wts, con
     if (zepp_layer_prepare_phase(l, 2, ids, wts, stream)) return 1;
   } else {
     if (zepp_layer_prepare_phase(l, 2, ids, wts, stream)) return 1;     // commits the step counter
-    if (zepp_layer_forward_phase(l, 0, x, y, stream)) return 1;
+    if (l->push_fork) {
+      // branch: push (reads only this rank's routing and x, writes the peers' staging) beside what follows
+      CU_OK(cudaEventRecord(l->ev_fork, (cudaStream_t)stream));
+      CU_OK(cudaStreamWaitEvent(l->push_stream, l->ev_fork, 0));
+      if (zepp_layer_forward_phase(l, 0, x, y, (void*)l->push_stream)) return 1;
+      CU_OK(cudaEventRecord(l->ev_join, l->push_stream));
+    } else {
+      if (zepp_layer_forward_phase(l, 0, x, y, stream)) return 1;
+    }
   }
   if (zepp_layer_prepare_phase(l, 3, ids, wts, stream)) return 1;
   l->fuse_x = nullptr;
-  for (int ph = 1; ph < 4; ++ph)
+  for (int ph = 1; ph < 4; ++ph) {
+    // the branch rejoins before the step's last kernel (the next step's push follows this step in order)
+    if (ph == 3 && l->push_fork) CU_OK(cudaStreamWaitEvent((cudaStream_t)stream, l->ev_join, 0));
     if (zepp_layer_forward_phase(l, ph, x, y, stream)) return 1;
+  }
   return 0;
 }
 
