@@ -156,7 +156,7 @@ __device__ __forceinline__ void st_global_v8(void* p, const uint32_t (&w)[8]) {
 }
 
 // ---------------------------------------------------------------------------------------
-// TMA (tiled 2D loads, no multicast anywhere in this library)
+// TMA (tiled 2D loads, each into the issuing CTA's own shared memory only)
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* tmap, uint64_t* bar, int c0,
                                             int c1) {
