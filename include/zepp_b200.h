@@ -60,6 +60,14 @@ int zepp_layer_set_placement(zepp_layer* layer, const int32_t* p2l, const int32_
 /* OverlapComm.set_weights (python/zepp/comm/overlap.py:95-100): w1 [gpe, ffn1, H], w2 [gpe, H, ffn] bf16 */
 int zepp_layer_set_weights(zepp_layer* layer, const void* w1_dev, const void* w2_dev);
 
+/* Token buckets of the serving path (python/zepp/serving.py:42-50, 687-734: every rank pads its step to a common
+ * bucket S_b <= max_tokens_per_rank): the following steps run at `tokens` rows per rank.  Every rank must choose
+ * the same value.  Buffers keep their size; zepp_layer_step keeps one captured graph per (bucket, pointers).
+ * Pad rows carry expert id -1 in topk_ids: such a copy has no owner, is counted in no load or split, moves no
+ * row and is not computed (the reference routes pad rows to local experts and subtracts them from the loads
+ * again, serving.py:147-160). */
+int zepp_layer_set_tokens(zepp_layer* layer, int tokens);
+
 /* WeightSlots (python/zepp/swap.py:236-300): with swap on, the layer owns the peer-visible weight slots
  * w1 [gpe, ffn1, H], w2 [gpe, H, ffn] that swapped experts travel between; callers fill them in place (or
  * pass their own tensors to zepp_layer_set_weights, which copies them in). */

@@ -25,17 +25,18 @@ def swiglu_fp32(h, ffn):
 
 @torch.no_grad()
 def moe_reference_fp32(x, ids, w, W1, W2):
-    """x [n, H]; ids [n, K] expert ids; w [n, K] fp32; W1 [E, 2I, H]; W2 [E, H, I] -> y fp32 [n, H]."""
+    """x [n, H]; ids [n, K] expert ids (negative: a pad copy, skipped); w [n, K] fp32; W1 [E, 2I, H]; W2 [E, H, I]
+    (tensors, or dicts holding the experts that occur) -> y fp32 [n, H]."""
     n, K = ids.shape
-    E, two_i, H = W1.shape
-    ffn = two_i // 2
+    H = x.shape[1]
     xf = x.float()
     y = torch.zeros(n, H, dtype=torch.float32)
     ids = ids.long()
-    for e in range(E):
-        rows, ks = (ids == e).nonzero(as_tuple=True)
-        if rows.numel() == 0:
+    for e in sorted(set(ids.reshape(-1).tolist())):
+        if e < 0:
             continue
+        rows, ks = (ids == e).nonzero(as_tuple=True)
+        ffn = W1[e].shape[0] // 2
         h = xf[rows] @ W1[e].float().t()
         a = swiglu_fp32(h, ffn)
         y.index_add_(0, rows, (a @ W2[e].float().t()) * w[rows, ks].float().unsqueeze(1))
@@ -53,6 +54,8 @@ def moe_reference_bf16_points(x, ids, w, W1, W2, act="swiglu"):
     ids = ids.long()
     bf = torch.bfloat16
     for e in torch.unique(ids).tolist():
+        if e < 0:
+            continue
         rows, ks = (ids == e).nonzero(as_tuple=True)
         w1, w2 = W1[e].float(), W2[e].float()
         h = (x[rows].float() @ w1.t()).to(bf)

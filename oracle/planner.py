@@ -383,16 +383,22 @@ def virtual_route(phys, nlp: int, gpe: int) -> np.ndarray:
 
 
 def routed_meta(vce: np.ndarray, R: int, S: int, gpe: int, NN: int, L: int):
-    """(splits [E_virt], scatter_index [R*S,K], sps [R,E_virt], uc [R, R+NN])."""
+    """(splits [E_virt], scatter_index [R*S,K], sps [R,E_virt], uc [R, R+NN]).
+
+    A negative entry is a pad copy: it is counted nowhere and gets scatter_index -1.  The reference planner
+    never sees such entries (its serving path routes pad rows to local experts, python/zepp/serving.py:106-160);
+    for real copies the result equals the reference's on the routing with the pad rows removed."""
     vce = np.asarray(vce, dtype=np.int64)
     ntok, K = vce.shape
     E_virt = R * gpe
     flat = vce.reshape(-1)
-    splits = np.bincount(flat, minlength=E_virt).astype(np.int32)
+    splits = np.bincount(flat[flat >= 0], minlength=E_virt).astype(np.int32)
     base = np.concatenate([[0], np.cumsum(splits)[:-1]]).astype(np.int64)
     nxt = base.copy()
-    scatter = np.empty(flat.shape[0], dtype=np.int32)
+    scatter = np.full(flat.shape[0], -1, dtype=np.int32)
     for n, e in enumerate(flat.tolist()):                    # stable rank in expert-sorted order
+        if e < 0:
+            continue
         scatter[n] = nxt[e]
         nxt[e] += 1
     sps = np.zeros((R, E_virt), dtype=np.int32)
@@ -401,6 +407,8 @@ def routed_meta(vce: np.ndarray, R: int, S: int, gpe: int, NN: int, L: int):
         s = t // S
         owners = set()
         for e in vce[t].tolist():
+            if e < 0:
+                continue
             sps[s, e] += 1
             owners.add(e // gpe)
         for o in owners:

@@ -1,5 +1,9 @@
-"""The MoE layer through the public API (EPMoE over the C-ABI) against the CPU oracle: planner
-products bit-exact, outputs within rtol 2e-2 / atol 2e-2 (bf16 inputs, fp32 accumulation)."""
+"""The MoE layer through the public API (EPMoE over the C-ABI) against the CPU oracle: planner products
+bit-exact; outputs within the stated rtol 2e-2 / atol 2e-2 of the fp32 reference path AND, because the outputs
+of N(0, 0.02) weights are themselves of the order of the tolerance, within a scale-aware bound of the oracle's
+bf16 path (same rounding points as the kernels): max |err| <= 1.5 % of the largest reference magnitude and a
+relative Frobenius error <= 0.5 %.  A halved output, a dropped expert contribution or a zeroed expert fail the
+second bound."""
 import dataclasses
 
 import numpy as np
@@ -11,11 +15,13 @@ from oracle import planner as op
 from zepp_b200 import EPMoE, EPMoEConfig, ModelShape
 from zepp_b200 import workloads as wl
 from zepp_b200.capacity import CapacityExceeded
-from zepp_b200.layer import LocalGroup, local_step, make_local_layers
+from zepp_b200.layer import LocalGroup, local_step, make_local_layers, token_buckets
 from zepp_b200.routing import Capacities
 
 pytestmark = pytest.mark.gpu
-RTOL = ATOL = 2e-2
+RTOL = ATOL = 2e-2            # the reference's check-path tolerance (bench/replay.py:154, examples/serving_check.py:353)
+MAX_REL_TO_SCALE = 1.5e-2     # against the bf16-points oracle, relative to max |reference|
+FRO_REL = 5e-3
 
 
 def _weights(shape):
@@ -24,14 +30,25 @@ def _weights(shape):
     return W1, W2
 
 
-def _reference(xs, ids, wts, W1, W2):
-    return [ol.moe_reference_fp32(xs[r], ids[r], wts[r], W1, W2) for r in range(len(xs))]
+def _close(y, x, ids, wts, W1, W2, tag, act="swiglu"):
+    """y (device or host, any float dtype) against both oracle paths on the same inputs."""
+    y = y.float().cpu()
+    if act == "swiglu":
+        ref32 = ol.moe_reference_fp32(x, ids, wts, W1, W2)
+        bad = ~torch.isclose(y, ref32, rtol=RTOL, atol=ATOL)
+        assert not bool(bad.any()), f"{tag}: {int(bad.sum())} of {bad.numel()} elements out of rtol/atol 2e-2, " \
+                                   f"max |err| {float((y - ref32).abs().max()):.4g}"
+    refb = ol.moe_reference_bf16_points(x, ids, wts, W1, W2, act=act).float()
+    scale = float(refb.abs().max())
+    err = float((y - refb).abs().max())
+    fro = float((y - refb).norm() / refb.norm().clamp_min(1e-30))
+    assert scale > 0 and err <= MAX_REL_TO_SCALE * scale and fro <= FRO_REL, \
+        f"{tag}: max |err| {err:.4g} vs scale {scale:.4g} (limit {MAX_REL_TO_SCALE * scale:.4g}), relative Frobenius {fro:.4g}"
 
 
-def _close(y, ref, tag):
-    bad = ~torch.isclose(y.float().cpu(), ref, rtol=RTOL, atol=ATOL)
-    assert not bool(bad.any()), f"{tag}: {int(bad.sum())} of {bad.numel()} elements out of tolerance, " \
-                               f"max |err| {float((y.float().cpu() - ref).abs().max()):.4g}"
+def _check_all(ys, xs, ids, wts, W1, W2, tag):
+    for r in range(len(xs)):
+        _close(ys[r], xs[r], ids[r], wts[r], W1, W2, f"{tag} rank{r}")
 
 
 def _run_local(shape, W, L, S, strategy, zipf=0.0, seed=0, steps=2, check_plan=True):
@@ -52,9 +69,7 @@ def _run_local(shape, W, L, S, strategy, zipf=0.0, seed=0, steps=2, check_plan=T
                             [x.cuda() for x in xs])
             for l in layers:
                 l.check()
-            refs = _reference(xs, ids, wts, W1, W2)
-            for r in range(W):
-                _close(ys[r], refs[r], f"{strategy} W{W} L{L} rank{r} step{step}")
+            _check_all(ys, xs, ids, wts, W1, W2, f"{strategy} W{W} L{L} step{step}")
             if check_plan:
                 pl0 = layers[0].placement
                 pl = op.Placement(pl0.p2l.numpy(), pl0.l2p.numpy(), pl0.lcnts.numpy())
@@ -124,7 +139,8 @@ def test_single_rank_gelu(strategy):
             e = int(ids[0, t, j])
             h = torch.nn.functional.gelu(x[t].float() @ W1[e].float().t())
             ref[t] += float(wts[0, t, j]) * (h @ W2[e].float().t())
-    _close(y, ref, f"gelu {strategy}")
+    assert torch.allclose(y.float().cpu(), ref, rtol=RTOL, atol=ATOL)
+    _close(y, x, ids[0], wts[0], W1, W2, f"gelu {strategy}", act="gelu")
     layer.close()
 
 
@@ -156,9 +172,7 @@ def test_fresh_payload_each_step_and_bitwise_repeat():
     for step in (0, 1, 0):
         xs = [wl.tokens(r, S, shape.hidden, seed=step) for r in range(W)]
         ys = local_step(layers, idc, wtc, [x.cuda() for x in xs])
-        refs = _reference(xs, ids, wts, W1, W2)
-        for r in range(W):
-            _close(ys[r], refs[r], f"step {step} rank {r}")
+        _check_all(ys, xs, ids, wts, W1, W2, f"step {step}")
         outs.append([y.clone() for y in ys])
     for r in range(W):
         assert torch.equal(outs[0][r], outs[2][r])
@@ -241,9 +255,7 @@ def test_swap_moves_weights_and_routes_on_the_new_placement():
                 assert layers[0].swap_moves == 0
             for l in layers:
                 assert np.array_equal(l.tables("p2l")[0].cpu().numpy(), cur.p2l), step
-            refs = _reference(xs, ids, wts, W1, W2)
-            for r in range(W):
-                _close(ys[r], refs[r], f"swap step {step} rank {r}")
+            _check_all(ys, xs, ids, wts, W1, W2, f"swap step {step}")
         assert total_moves > 0, "the skewed routing never triggered a swap"
     finally:
         for l in layers:
@@ -273,8 +285,7 @@ def test_full_size_benchmark_step_sampled_against_oracle():
     sample = torch.arange(0, S, 16)
     W1 = torch.stack([wdev[e][0].cpu() for e in range(shape.num_experts)])
     W2 = torch.stack([wdev[e][1].cpu() for e in range(shape.num_experts)])
-    ref = ol.moe_reference_fp32(x[sample], ids[0][sample], wts[0][sample], W1, W2)
-    _close(y[sample.cuda()], ref, "full-size sample")
+    _close(y[sample.cuda()], x[sample], ids[0][sample], wts[0][sample], W1, W2, "full-size sample")
     layer.close()
 
 
@@ -303,9 +314,7 @@ def test_trace_replay_batch_through_the_layer():
         ys = local_step(layers, [ids[r].cuda() for r in range(W)], [wts[r].cuda() for r in range(W)], [x.cuda() for x in xs])
         for l in layers:
             l.check()
-        refs = _reference(xs, ids, wts, W1, W2)
-        for r in range(W):
-            _close(ys[r], refs[r], f"trace replay rank{r}")
+        _check_all(ys, xs, ids, wts, W1, W2, "trace replay")
         pl0 = layers[0].placement
         pl = op.Placement(pl0.p2l.numpy(), pl0.l2p.numpy(), pl0.lcnts.numpy())
         phys, _ = op.reference_route(ids.numpy(), pl, cfg.slots_per_rank, W, cfg.router_c)

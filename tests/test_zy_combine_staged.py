@@ -1,7 +1,6 @@
-"""The combine GEMM's line-staged epilogue (ZEPP_B200_COMBINE_STAGED=1: rows staged per warp in shared memory,
-whole 128-byte lines stored) under the layer's own parity tests.  The switch is read when a layer is created,
-so the parity tests run again in a child process with it set.  Expected to fail rather than failing the suite
-until the variant has had its first GPU run: it was written after the GPU budget of its round was spent."""
+"""The combine GEMM's two epilogue forms under the layer's own parity tests.  The form is chosen when a layer is
+created (ZEPP_B200_COMBINE_STAGED: unset = staged lines whenever rows cross to other ranks, "1" = always staged,
+"0" = never), so the parity tests run again in child processes with each forced setting."""
 import os
 import subprocess
 import sys
@@ -12,9 +11,9 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-@pytest.mark.xfail(strict=False, reason="first GPU run of the line-staged combine epilogue")
-def test_layer_parity_with_line_staged_combine_epilogue():
-    env = dict(os.environ, ZEPP_B200_COMBINE_STAGED="1")
+@pytest.mark.parametrize("forced", ["1", "0"])
+def test_layer_parity_with_forced_combine_epilogue(forced):
+    env = dict(os.environ, ZEPP_B200_COMBINE_STAGED=forced)
     sel = "emulated_ranks or odd_number or single_rank_small or many_rows or repeat or trace_replay"
     r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(ROOT, "tests", "test_layer_gpu.py"), "-m", "gpu",
                         "-x", "-q", "-k", sel], env=env, capture_output=True, text=True, timeout=900, cwd=ROOT)

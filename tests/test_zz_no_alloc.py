@@ -13,6 +13,7 @@ import numpy as np
 import pytest
 import torch
 
+from oracle import planner as op
 from zepp_b200._ext import check, lib
 
 pytestmark = pytest.mark.gpu
@@ -60,6 +61,11 @@ def test_noalloc_matches_workspace_variant_twice_in_a_row():
             for name in NAMES:
                 assert np.array_equal(got[name], ref[name]), (R, L, S, K, gpe, rank, name)
             assert int(ref["splits"].sum()) == R * S * K and ref["demands"][7] == 0
+        # and against the CPU oracle directly, so this file stands on its own
+        splits, scat, sps, uc = op.routed_meta(vce_in.cpu().numpy().reshape(R * S, K), R, S, gpe, R // L, L)
+        assert np.array_equal(got["splits"], splits) and np.array_equal(got["scatter_index"], scat.reshape(-1))
+        assert np.array_equal(got["sps"], sps.reshape(-1)) and np.array_equal(got["uc"], uc.reshape(-1))
+        assert got["demands"][:7].tolist() == op.demands_from_meta(sps, uc, R, L, gpe)
 
 
 def test_noalloc_refuses_routings_beyond_its_scratch():

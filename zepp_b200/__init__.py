@@ -13,6 +13,7 @@ tokens_per_rank = _config.tokens_per_rank
 EPMoE = _layer.EPMoE
 Marks = _layer.Marks
 activation = _layer.activation
+token_buckets = _layer.token_buckets
 
-__all__ = ["SHAPES", "ModelShape", "EPMoEConfig", "tokens_per_rank", "EPMoE", "Marks", "activation"]
+__all__ = ["SHAPES", "ModelShape", "EPMoEConfig", "tokens_per_rank", "EPMoE", "Marks", "activation", "token_buckets"]
 __version__ = "0.1.0"

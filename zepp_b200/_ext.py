@@ -13,7 +13,7 @@ SYMBOLS = (
     "zepp_last_error", "zepp_abi_version", "zepp_rt_create", "zepp_rt_destroy", "zepp_rt_ipc_handle",
     "zepp_rt_open_peers", "zepp_rt_link_local", "zepp_rt_set_wait_limit_ms", "zepp_rt_sm_count",
     "zepp_layer_arena_bytes", "zepp_layer_create", "zepp_layer_destroy", "zepp_layer_set_placement",
-    "zepp_layer_set_weights", "zepp_layer_weight_slots", "zepp_layer_prepare", "zepp_layer_prepare_phase", "zepp_layer_forward",
+    "zepp_layer_set_weights", "zepp_layer_set_tokens", "zepp_layer_weight_slots", "zepp_layer_prepare", "zepp_layer_prepare_phase", "zepp_layer_forward",
     "zepp_layer_forward_phase", "zepp_layer_step", "zepp_layer_status", "zepp_layer_trace", "zepp_layer_table", "zepp_layer_gpu_launches",
     "zepp_route_workspace_ints", "zepp_route_ws_offsets", "zepp_route", "zepp_meta_workspace_bytes",
     "zepp_routed_meta", "zepp_routed_meta_noalloc", "zepp_dispatch_plan_words", "zepp_swap_decide_out_ints", "zepp_swap_decide",

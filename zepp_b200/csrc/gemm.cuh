@@ -87,7 +87,7 @@ struct GemmArgs {
   int gather;                              // 1: run the gather warps and gate tiles on tile_ready
   // bounded waits
   unsigned long long* status;
-  unsigned int mbar_limit;
+  unsigned long long mbar_limit_ns;   // inner (mbarrier) waits enclose the cross-rank waits: bounded later than those
   unsigned long long flag_limit_ns;
 };
 
@@ -235,7 +235,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             const int stage0 = stage;
             bool ok = true;
             for (int kb = 0; kb < pre && ok; ++kb) {
-              if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abortp, a.mbar_limit)) {
+              if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abortp, a.mbar_limit_ns)) {
                 record_timeout(a.status, WAIT_MBAR_EMPTY, item, kb);
                 ok = false;
                 break;
@@ -273,7 +273,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
           if (item == item_first) trace_mark_max(a.status, TR_FIRST_ITEMS);
         }
         for (int kb = kb_first; kb < k_blocks; ++kb) {
-          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abortp, a.mbar_limit)) {
+          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abortp, a.mbar_limit_ns)) {
             record_timeout(a.status, WAIT_MBAR_EMPTY, item, kb);
             abort_flag = 1;
             break;
@@ -302,7 +302,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
       ZEPP_PROF(long long prof_data = 0; long long prof_acc = 0; long long prof_t;)
       for (int item = item_first; item < total_items && !*abortp; item += item_stride) {
         ZEPP_PROF(prof_t = clock64();)
-        if (!mbar_wait_bounded(&acc_empty_bar[acc], acc_phase ^ 1, abortp, a.mbar_limit)) {
+        if (!mbar_wait_bounded(&acc_empty_bar[acc], acc_phase ^ 1, abortp, a.mbar_limit_ns)) {
           record_timeout(a.status, WAIT_TMEM_EMPTY, item, acc);
           abort_flag = 1;
           break;
@@ -313,7 +313,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         bool ok = true;
         for (int kb = 0; kb < k_blocks; ++kb) {
           ZEPP_PROF(prof_t = clock64();)
-          if (!mbar_wait_bounded(&full_bar[stage], phase, abortp, a.mbar_limit)) {
+          if (!mbar_wait_bounded(&full_bar[stage], phase, abortp, a.mbar_limit_ns)) {
             record_timeout(a.status, WAIT_MBAR_FULL, item, kb);
             abort_flag = 1;
             ok = false;
@@ -373,7 +373,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
       }
       int got = 1;
       if (lane == 0) {
-        got = mbar_wait_bounded(&acc_full_bar[acc], acc_phase, abortp, a.mbar_limit) ? 1 : 0;
+        got = mbar_wait_bounded(&acc_full_bar[acc], acc_phase, abortp, a.mbar_limit_ns) ? 1 : 0;
         if (!got && !*abortp) {
           record_timeout(a.status, WAIT_TMEM_FULL, item, acc);
           abort_flag = 1;

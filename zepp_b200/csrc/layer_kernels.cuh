@@ -38,22 +38,31 @@ __global__ void publish_x_kernel(const uint4* __restrict__ x, uint4* __restrict_
 // across NVLink.  A block owns a range of tokens; it recounts the slots of the tokens before its
 // range from phys_own (a few KB) instead of waiting for another block.
 struct PushArgs {
-  const int* phys_own;                 // [S, K]
+  const int* phys_own;                 // [S, K] physical slots of this rank's copies, or nullptr:
+  const int* topk_own;                 //   then [S, K] expert ids looked up in slot_of (single-replica placements)
+  const int* slot_of;                  // [G]
+  int G;
   const __nv_bfloat16* x;              // [S, H]
-  PeerTable stage;                     // rank p's staging buffer base [W, S, H]
+  PeerTable stage;                     // rank p's staging buffer base [W, region_tokens, H]
   PeerTable flags;                     // rank p's push-arrival words [W]
   int S, K, H, nlp, rank, world;
+  int region_tokens;                   // rows of one source's staging region (the layer's largest bucket)
   const unsigned long long* epoch_ptr;
   unsigned int* counter;
   unsigned long long* status;
 };
 
-__global__ void __launch_bounds__(256) dispatch_push_kernel(PushArgs a) {
+constexpr int kPushMaxTokensPerBlock = 256;
+
+// One block's share of the push: tokens [blk * tpb, (blk + 1) * tpb) of `nblk` equal ranges.  `epoch` is the
+// step's epoch; the last of the nblk blocks to finish raises this rank's push flag on every rank.
+__device__ void push_block(const PushArgs& a, int blk, int nblk, unsigned long long epoch) {
   __shared__ int before[kMaxRanks];      // tokens before this block's range that go to rank d
-  __shared__ unsigned long long tmask[64];
-  const unsigned long long epoch = step_epoch(a.epoch_ptr, false);
-  const int tpb = (a.S + gridDim.x - 1) / gridDim.x;          // tokens per block (<= 64)
-  const int t_lo = blockIdx.x * tpb;
+  __shared__ unsigned long long tmask[kPushMaxTokensPerBlock];
+  __shared__ unsigned int dbits[kMaxRanks][kPushMaxTokensPerBlock / 32];   // bit t of row d: token t of the range goes to rank d
+  __shared__ int wpre[kMaxRanks][kPushMaxTokensPerBlock / 32];             // such tokens in the earlier 32-token words
+  const int tpb = (a.S + nblk - 1) / nblk;                    // tokens per block (<= kPushMaxTokensPerBlock)
+  const int t_lo = min(a.S, blk * tpb);
   const int t_hi = min(a.S, t_lo + tpb);
   for (int d = threadIdx.x; d < a.world; d += blockDim.x) before[d] = 0;
   __syncthreads();
@@ -61,7 +70,13 @@ __global__ void __launch_bounds__(256) dispatch_push_kernel(PushArgs a) {
   for (int t = threadIdx.x; t < t_hi; t += blockDim.x) {
     unsigned long long m = 0;
     for (int k = 0; k < a.K; ++k) {
-      const int p = a.phys_own[t * a.K + k];
+      int p;
+      if (a.phys_own != nullptr) {
+        p = a.phys_own[t * a.K + k];
+      } else {
+        const int e = a.topk_own[t * a.K + k];
+        p = (e >= 0 && e < a.G) ? a.slot_of[e] : -1;
+      }
       if (p >= 0) m |= 1ull << (p / a.nlp);
     }
     if (t < t_lo) {
@@ -71,16 +86,29 @@ __global__ void __launch_bounds__(256) dispatch_push_kernel(PushArgs a) {
     }
   }
   __syncthreads();
-  // one warp per (token, destination) row
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int n_tok = t_hi - t_lo, n_words = (n_tok + 31) / 32;
+  for (int w = wid; w < n_words; w += nw) {
+    const unsigned long long m = 32 * w + lane < n_tok ? tmask[32 * w + lane] : 0ull;
+    for (int d = 0; d < a.world; ++d) {
+      const unsigned int bits = __ballot_sync(0xffffffffu, (m >> d) & 1ull);
+      if (lane == 0) dbits[d][w] = bits;
+    }
+  }
+  __syncthreads();
+  for (int d = threadIdx.x; d < a.world; d += blockDim.x) {
+    int run = before[d];
+    for (int w = 0; w < n_words; ++w) { wpre[d][w] = run; run += __popc(dbits[d][w]); }
+  }
+  __syncthreads();
+  // one warp per (token, destination) row
   const int vec_per_row = a.H / 8;
-  const size_t region = (size_t)a.rank * a.S * a.H;
+  const size_t region = (size_t)a.rank * a.region_tokens * a.H;
   for (int pair = wid; pair < (t_hi - t_lo) * a.world; pair += nw) {
     const int tl = pair / a.world, d = pair - tl * a.world;
     const unsigned long long m = tmask[tl];
     if (!((m >> d) & 1ull)) continue;
-    int slot = before[d];
-    for (int q = 0; q < tl; ++q) slot += (int)((tmask[q] >> d) & 1ull);
+    const int slot = wpre[d][tl >> 5] + __popc(dbits[d][tl >> 5] & ((1u << (tl & 31)) - 1u));
     const uint4* sp = reinterpret_cast<const uint4*>(a.x + (size_t)(t_lo + tl) * a.H);
     uint4* dp = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.stage.ptr[d]) + region + (size_t)slot * a.H);
     for (int v0 = 0; v0 < vec_per_row; v0 += 256) {
@@ -100,13 +128,17 @@ __global__ void __launch_bounds__(256) dispatch_push_kernel(PushArgs a) {
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence_system();
-    const unsigned int prev = atomicInc(a.counter, gridDim.x - 1);
-    if (prev == gridDim.x - 1) {
+    const unsigned int prev = atomicInc(a.counter, nblk - 1);
+    if (prev == (unsigned int)nblk - 1) {
       __threadfence_system();
       for (int p = 0; p < a.world; ++p)
         st_relaxed_sys(reinterpret_cast<unsigned long long*>(a.flags.ptr[p]) + a.rank, epoch);
     }
   }
+}
+
+__global__ void __launch_bounds__(256) dispatch_push_kernel(PushArgs a) {
+  push_block(a, blockIdx.x, gridDim.x, step_epoch(a.epoch_ptr, false));
 }
 
 struct MoveArgs {

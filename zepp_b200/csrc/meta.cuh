@@ -6,14 +6,20 @@
 // (src/planner/lane_device.cu:526-540) and the combine tables (src/combine/combine_kernels.cu:1308,1546);
 // host references python/zepp/routing.py:306-331, python/zepp/capacity.py:30-55.
 //
-// Three launches, no atomics on global memory, no host read:
-//   pass1  one block per tile of one source's entries: vce / probs_all (from the gathered routing
+// No atomics on global memory beyond one arrival counter, no host read.  Three stages:
+//   count  one block per tile of one source's entries: vce / probs_all (from the gathered routing
 //          rows), per-tile expert histogram, per-tile unique owner / node counts;
-//   scan   one block: splits, sps, uc, exclusive bases (tile histograms become tile bases in
-//          place), demands + mask, plan heads, this rank's tile schedule;
-//   pass2  same grid as pass1: stable rank of every copy inside its expert (warps of a tile take
-//          turns, lanes rank themselves with match_any), scatter_index, and for copies owned by
-//          this rank the GEMM row tables (source token, home slot, top-k weight).
+//   scan   splits, sps, uc, exclusive bases, demands + mask, plan heads, this rank's tile schedule;
+//   rank   stable rank of every copy inside its expert (warps of a tile take turns, lanes rank
+//          themselves with match_any), scatter_index, and for copies owned by this rank the GEMM row
+//          tables (source token, home slot, top-k weight).
+// meta_fused_kernel runs all three in ONE cooperative launch (count -> grid barrier -> every tile block
+// derives its own bases from the per-tile counts and ranks its copies, while one extra block writes the
+// step's tables); meta_pass1_kernel (count + scan in its last block) and meta_pass2_kernel (rank) are the
+// two-launch form for grids too large to be co-resident.
+//
+// A copy whose expert id is negative is a PAD copy (the rows a caller adds to fill a token bucket): it has
+// no owner, is counted nowhere, moves no row and gets vce = scatter_index = -1.
 #pragma once
 #include "common.cuh"
 #include "planner.cuh"
@@ -79,10 +85,48 @@ struct MetaArgs {
   unsigned long long limit_ns;
   unsigned long long* status;
   unsigned int* block_counter;   // pass1: the last block to finish runs the scan
+  unsigned int* grid_sync;       // fused kernel: [0] self-resetting arrival counter, [1] release generation
 };
 
-__device__ void meta_scan_body(MetaArgs& a, int* chunks);
+__device__ void meta_scan_body(MetaArgs& a, int* chunks, bool bases_in_place);
 __device__ void plan_heads(MetaArgs& a, const int* chunks, const int* s_uc);
+
+// Virtual group of entry n of source `src` (-1: a pad copy).  Writes vce (and probs_all when the routing
+// rows carry weights); on one rank with a single-replica placement it also does the slot lookup and
+// writes the routing rows themselves.
+__device__ __forceinline__ int meta_decode_entry(const MetaArgs& a, bool local, int src, int n, int SK, int E_virt) {
+  const size_t flat = (size_t)src * SK + n;
+  int v;
+  if (local) {
+    const int e = a.local_topk[n];
+    int phys = -1;
+    if (e >= a.G) {
+      if (a.status) atomicOr(a.status + ST_ERROR, (unsigned long long)ERR_BAD_INDEX);
+    } else if (e >= 0 && (phys = a.slot_of[e]) < 0) {
+      if (a.status) atomicOr(a.status + ST_ERROR, (unsigned long long)ERR_ROUTE);
+      phys = -1;
+    }
+    const float w = a.local_probs[n];
+    a.phys_own[n] = phys;
+    a.send_row[n] = phys; a.send_row[SK + n] = __float_as_int(w);
+    a.gathered_out[n] = phys; a.gathered_out[SK + n] = __float_as_int(w);
+    a.probs_all[flat] = w;
+    v = phys < 0 ? -1 : (phys / a.nlp) * a.gpe + 1 + phys % a.nlp;
+  } else if (a.gathered) {
+    const int phys = a.gathered[(size_t)src * 2 * SK + n];
+    v = phys < 0 ? -1 : (phys / a.nlp) * a.gpe + 1 + phys % a.nlp;
+    a.probs_all[flat] = __int_as_float(a.gathered[(size_t)src * 2 * SK + SK + n]);
+  } else {
+    v = a.vce_in[flat];
+    if (v < 0) v = -1;
+  }
+  if (v >= E_virt) {
+    if (a.status) atomicOr(a.status + ST_ERROR, (unsigned long long)ERR_BAD_INDEX);
+    v = 0;
+  }
+  a.vce[flat] = v;
+  return v;
+}
 
 __global__ void __launch_bounds__(kMetaThreads) meta_pass1_kernel(MetaArgs a) {
   extern __shared__ int sm[];
@@ -109,36 +153,8 @@ __global__ void __launch_bounds__(kMetaThreads) meta_pass1_kernel(MetaArgs a) {
   const int n_lo = tb * T;
   const int n_hi = min(SK, n_lo + T);
   for (int n = n_lo + threadIdx.x; n < n_hi; n += blockDim.x) {
-    int v;
-    const size_t flat = (size_t)src * SK + n;
-    if (local) {
-      const int e = a.local_topk[n];
-      int phys = 0;
-      if (e < 0 || e >= a.G) {
-        if (a.status) atomicOr(a.status + ST_ERROR, (unsigned long long)ERR_BAD_INDEX);
-      } else if ((phys = a.slot_of[e]) < 0) {
-        if (a.status) atomicOr(a.status + ST_ERROR, (unsigned long long)ERR_ROUTE);
-        phys = 0;
-      }
-      const float w = a.local_probs[n];
-      a.phys_own[n] = phys;
-      a.send_row[n] = phys; a.send_row[SK + n] = __float_as_int(w);
-      a.gathered_out[n] = phys; a.gathered_out[SK + n] = __float_as_int(w);
-      a.probs_all[flat] = w;
-      v = (phys / a.nlp) * a.gpe + 1 + phys % a.nlp;
-    } else if (a.gathered) {
-      const int phys = a.gathered[(size_t)src * 2 * SK + n];
-      v = (phys / a.nlp) * a.gpe + 1 + phys % a.nlp;
-      a.probs_all[flat] = __int_as_float(a.gathered[(size_t)src * 2 * SK + SK + n]);
-    } else {
-      v = a.vce_in[flat];
-    }
-    if (v < 0 || v >= E_virt) {
-      if (a.status) atomicOr(a.status + ST_ERROR, (unsigned long long)ERR_BAD_INDEX);
-      v = 0;
-    }
-    a.vce[flat] = v;
-    atomicAdd(&hist[v], 1);
+    const int v = meta_decode_entry(a, local, src, n, SK, E_virt);
+    if (v >= 0) atomicAdd(&hist[v], 1);
   }
   __syncthreads();
   // unique owners / nodes per token (a token may pick one rank several times)
@@ -147,7 +163,9 @@ __global__ void __launch_bounds__(kMetaThreads) meta_pass1_kernel(MetaArgs a) {
   for (int t = t_lo + threadIdx.x; t < t_hi; t += blockDim.x) {
     unsigned long long owners = 0, nodes = 0;
     for (int k = 0; k < a.K; ++k) {
-      const int o = a.vce[((size_t)src * a.S + t) * a.K + k] / a.gpe;
+      const int v = a.vce[((size_t)src * a.S + t) * a.K + k];
+      if (v < 0) continue;                       // pad copy
+      const int o = v / a.gpe;
       owners |= 1ull << o;
       nodes |= 1ull << (o / a.L);
     }
@@ -167,7 +185,7 @@ __global__ void __launch_bounds__(kMetaThreads) meta_pass1_kernel(MetaArgs a) {
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  meta_scan_body(a, sm);
+  meta_scan_body(a, sm, true);
   // every block has read the counter by now (they all arrived before this block was chosen)
   if (local && threadIdx.x == 0 && a.ctr != nullptr) *a.ctr = epoch;
 }
@@ -270,7 +288,7 @@ __host__ __device__ inline size_t meta_scan_smem_ints(int R, int NN, int E_virt)
   return (size_t)R * R + (size_t)R * (R + NN) + 2 * (size_t)E_virt + 1;
 }
 
-__device__ void meta_scan_body(MetaArgs& a, int* sm) {
+__device__ void meta_scan_body(MetaArgs& a, int* sm, bool bases_in_place) {
   const int R = a.R, NN = a.R / a.L, E_virt = a.R * a.gpe, ucw = R + NN;
   const int n_blocks = R * a.tiles_per_src;
   int* chunks = sm;
@@ -289,7 +307,7 @@ __device__ void meta_scan_body(MetaArgs& a, int* sm) {
     const int d = e / a.gpe;
     for (int s = 0; s < R; ++s) {
       int acc = 0;
-      for (int tb = 0; tb < a.tiles_per_src; ++tb) acc += a.tile_hist[(size_t)(s * a.tiles_per_src + tb) * E_virt + e];
+      for (int tb = 0; tb < a.tiles_per_src; ++tb) acc += __ldcg(a.tile_hist + (size_t)(s * a.tiles_per_src + tb) * E_virt + e);
       a.sps[s * E_virt + e] = acc;
       if (acc) atomicAdd(&chunks[s * R + d], acc);
       tot += acc;
@@ -300,7 +318,7 @@ __device__ void meta_scan_body(MetaArgs& a, int* sm) {
   for (int i = threadIdx.x; i < R * ucw; i += blockDim.x) {
     const int s = i / ucw, d = i - s * ucw;
     int acc = 0;
-    for (int tb = 0; tb < a.tiles_per_src; ++tb) acc += a.tile_uc[(size_t)(s * a.tiles_per_src + tb) * ucw + d];
+    for (int tb = 0; tb < a.tiles_per_src; ++tb) acc += __ldcg(a.tile_uc + (size_t)(s * a.tiles_per_src + tb) * ucw + d);
     a.uc[i] = acc;
     s_uc[i] = acc;
   }
@@ -321,6 +339,7 @@ __device__ void meta_scan_body(MetaArgs& a, int* sm) {
   }
   __syncthreads();
   if (threadIdx.x == 0) trace_mark(a.status, TR_SCAN_BASES);
+  if (bases_in_place)
   for (int e = threadIdx.x; e < E_virt; e += blockDim.x) {      // tile histograms -> tile bases, in place
     int run = s_base[e];
     for (int b = 0; b < n_blocks; ++b) {
@@ -509,12 +528,14 @@ __global__ void __launch_bounds__(kMetaThreads) meta_pass2_kernel(MetaArgs a) {
   const int n = tb * T + threadIdx.x;
   const bool valid = threadIdx.x < T && n < SK;
   const size_t flat = (size_t)src * SK + (valid ? n : 0);
-  const int e = valid ? a.vce[flat] : -1 - (int)(threadIdx.x & 31);     // invalid lanes never match
+  int e = valid ? a.vce[flat] : -1;
+  const bool pad = valid && e < 0;
+  if (e < 0) e = -1 - (int)(threadIdx.x & 31);                          // invalid lanes and pad copies never match
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   unsigned m = 0;
   if (wid < n_warps) {
     m = __match_any_sync(0xffffffffu, e);
-    if (valid && lane == __ffs(m) - 1) wc[wid * E_virt + e] = __popc(m);
+    if (valid && !pad && lane == __ffs(m) - 1) wc[wid * E_virt + e] = __popc(m);
   }
   __syncthreads();
   for (int x = threadIdx.x; x < E_virt; x += blockDim.x) {      // exclusive prefix over the tile's warps
@@ -535,7 +556,7 @@ __global__ void __launch_bounds__(kMetaThreads) meta_pass2_kernel(MetaArgs a) {
     const int tpt = a.tokens_per_tile;
     for (int t = threadIdx.x; t < tpt; t += blockDim.x) s_tokslot[t] = 0;
     __syncthreads();
-    if (valid && e / a.gpe == a.my_rank) s_tokslot[threadIdx.x / a.K] = 1;
+    if (valid && !pad && e / a.gpe == a.my_rank) s_tokslot[threadIdx.x / a.K] = 1;
     __syncthreads();
     const int f = threadIdx.x < tpt ? s_tokslot[threadIdx.x] : 0;
     int total;
@@ -547,6 +568,7 @@ __global__ void __launch_bounds__(kMetaThreads) meta_pass2_kernel(MetaArgs a) {
     __syncthreads();
   }
   if (!valid) return;
+  if (pad) { a.scatter_index[flat] = -1; return; }
   const int idx = wc[wid * E_virt + e] + __popc(m & ((1u << lane) - 1u));
   a.scatter_index[flat] = idx;
   if (a.row_tok != nullptr && e / a.gpe == a.my_rank) {
@@ -557,6 +579,15 @@ __global__ void __launch_bounds__(kMetaThreads) meta_pass2_kernel(MetaArgs a) {
       a.row_dst[r] = ((long long)src << 40) | ((long long)n * a.hidden);
     }
   }
+}
+
+// Shared memory of the fused kernel (ints): the larger of a tile block's tables
+// (hist[E] | ucs[R+NN] | tot[E] | base[E+1] | v[threads] | wc[max(warps, 16) * E]) and the tables block's scan.
+__host__ __device__ inline size_t meta_fused_smem_ints(int R, int NN, int E_virt, int tokens_per_tile, int K) {
+  const int n_warps = (tokens_per_tile * K + 31) / 32;
+  const size_t tile = 3 * (size_t)E_virt + (size_t)(R + NN) + 1 + kMetaThreads + (size_t)(n_warps > 16 ? n_warps : 16) * E_virt;
+  const size_t scan = meta_scan_smem_ints(R, NN, E_virt);
+  return tile > scan ? tile : scan;
 }
 
 }  // namespace zepp

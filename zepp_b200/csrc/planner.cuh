@@ -67,7 +67,7 @@ __global__ void loads_publish_kernel(const int* __restrict__ topk_own, int n_ent
   for (int n = threadIdx.x; n < n_entries; n += blockDim.x) {
     const int g = topk_own[n];
     if (g >= 0 && g < G) atomicAdd(&hist[g], 1);
-    else if (status) atomicOr(status + ST_ERROR, (unsigned long long)ERR_BAD_INDEX);
+    else if (g >= G && status) atomicOr(status + ST_ERROR, (unsigned long long)ERR_BAD_INDEX);   // negative: a pad copy
   }
   __syncthreads();
   for (int p = 0; p < world; ++p) {
@@ -141,7 +141,7 @@ __global__ void __launch_bounds__(256) route_kernel(RouteArgs a) {
   if (a.topk_own != nullptr)
   for (int n = blockIdx.x * blockDim.x + threadIdx.x; n < a.n_entries; n += gridDim.x * blockDim.x) {
     const int e = a.topk_own[n];
-    if (e < 0 || e >= G) continue;
+    if (e < 0 || e >= G) { a.phys_own[n] = -1; continue; }     // pad copy (or an id the loads kernel reported)
     const int cnt = min(a.lcnts[e], R);
     int found = 0, p0 = -1;
     for (int j = 0; j < cnt; ++j) {
@@ -336,7 +336,7 @@ struct FinishArgs {
   PeerTable flags;         // rank p's arrival words [R]
   int world;               // ranks to publish to (0: none)
   const unsigned long long* epoch_ptr;
-  unsigned int* block_counter;
+  unsigned int* block_counter;   // self-resetting arrival counter of the grid (nullptr: launched as one block)
   unsigned long long* status;
   long long* stats;
 };
@@ -361,7 +361,7 @@ __device__ void vacate_serial(const FinishArgs& a) {
     const int* tk = a.topk_own + s * K;
     bool any_remote = false;
     for (int k = 0; k < Kc; ++k) {
-      node_of[k] = ph[k] / nlp / L;
+      node_of[k] = ph[k] < 0 ? home : ph[k] / nlp / L;          // a pad copy is never remote
       any_remote |= node_of[k] != home;
     }
     if (!any_remote) continue;
@@ -447,8 +447,8 @@ __global__ void route_finish_kernel(FinishArgs a) {
   __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
-    const unsigned int prev = atomicInc(a.block_counter, gridDim.x - 1);
-    if (prev == gridDim.x - 1) {
+    const bool last = a.block_counter == nullptr || atomicInc(a.block_counter, gridDim.x - 1) == gridDim.x - 1;
+    if (last) {
       __threadfence_system();
       for (int p = 0; p < a.world; ++p)
         if (a.flags.ptr[p]) st_relaxed_sys(reinterpret_cast<unsigned long long*>(a.flags.ptr[p]) + a.my_rank, epoch);
@@ -486,14 +486,15 @@ struct SimpleRouteArgs {
 };
 
 __device__ __forceinline__ int single_replica_slot(const SimpleRouteArgs& a, const int* slots, int e) {
-  if (e < 0 || e >= a.G) {
+  if (e < 0) return -1;                    // pad copy: no slot, no owner
+  if (e >= a.G) {
     if (a.status) atomicOr(a.status + ST_ERROR, (unsigned long long)ERR_BAD_INDEX);
-    return 0;
+    return -1;
   }
   const int p = slots[e];
   if (p < 0) {
     if (a.status) atomicOr(a.status + ST_ERROR, (unsigned long long)ERR_ROUTE);
-    return 0;
+    return -1;
   }
   return p;
 }
@@ -509,6 +510,50 @@ __global__ void slot_table_kernel(const int* l2p, const int* lcnts, int G, int R
   slot_of[e] = p0;
 }
 
+// Rows [blk, nblk) of the single-replica routing: slot lookup, local copies, and the send row [phys | weight
+// bits] into every rank's gather table.  `slots` is a shared-memory copy of slot_of.
+__device__ void route_simple_rows(const SimpleRouteArgs& a, const int* slots, int blk, int nblk,
+                                  unsigned long long epoch) {
+  const PeerTable& dst = (epoch & 1) ? a.dst_odd : a.dst;
+  const int* wbits = reinterpret_cast<const int*>(a.probs_own);
+  const int SK = a.SK;
+  const size_t row_off = (size_t)a.my_rank * 2 * SK;
+  if ((SK & 3) == 0) {
+    // four entries per thread, 16-byte stores into every rank's gather table
+    for (int q = blk * blockDim.x + threadIdx.x; q < SK / 4; q += nblk * blockDim.x) {
+      const int4 e4 = reinterpret_cast<const int4*>(a.topk_own)[q];
+      const int4 w4 = reinterpret_cast<const int4*>(wbits)[q];
+      int4 p4;
+      p4.x = single_replica_slot(a, slots, e4.x);
+      p4.y = single_replica_slot(a, slots, e4.y);
+      p4.z = single_replica_slot(a, slots, e4.z);
+      p4.w = single_replica_slot(a, slots, e4.w);
+      reinterpret_cast<int4*>(a.phys_own)[q] = p4;
+      if (a.send_row) {
+        reinterpret_cast<int4*>(a.send_row)[q] = p4;
+        reinterpret_cast<int4*>(a.send_row + SK)[q] = w4;
+      }
+      for (int p = 0; p < a.world; ++p) {
+        int* row = reinterpret_cast<int*>(dst.ptr[p]) + row_off;
+        reinterpret_cast<int4*>(row)[q] = p4;
+        reinterpret_cast<int4*>(row + SK)[q] = w4;
+      }
+    }
+  } else {
+    for (int n = blk * blockDim.x + threadIdx.x; n < SK; n += nblk * blockDim.x) {
+      const int p0 = single_replica_slot(a, slots, a.topk_own[n]);
+      const int wb = wbits[n];
+      a.phys_own[n] = p0;
+      if (a.send_row) { a.send_row[n] = p0; a.send_row[SK + n] = wb; }
+      for (int p = 0; p < a.world; ++p) {
+        int* row = reinterpret_cast<int*>(dst.ptr[p]) + row_off;
+        row[n] = p0;
+        row[SK + n] = wb;
+      }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256) route_simple_publish_kernel(SimpleRouteArgs a) {
   const unsigned long long epoch = step_epoch(a.ctr, a.first != 0);
   if (blockIdx.x == 0 && threadIdx.x == 0) {
@@ -519,52 +564,13 @@ __global__ void __launch_bounds__(256) route_simple_publish_kernel(SimpleRouteAr
   if ((int)blockIdx.x < a.route_blocks) {
     for (int g = threadIdx.x; g < a.G; g += blockDim.x) slots[g] = a.slot_of[g];
     __syncthreads();
-  }
-  if ((int)blockIdx.x >= a.route_blocks) {
+    route_simple_rows(a, slots, blockIdx.x, a.route_blocks, epoch);
+  } else {
     // x publication blocks
     uint4* xsym = (epoch & 1) ? a.xsym_odd : a.xsym_even;
     const size_t nb = gridDim.x - a.route_blocks;
     for (size_t i = (size_t)(blockIdx.x - a.route_blocks) * blockDim.x + threadIdx.x; i < a.x_vec; i += nb * blockDim.x)
       xsym[i] = a.x[i];
-  } else {
-    const PeerTable& dst = (epoch & 1) ? a.dst_odd : a.dst;
-    const int* wbits = reinterpret_cast<const int*>(a.probs_own);
-    const int SK = a.SK;
-    const size_t row_off = (size_t)a.my_rank * 2 * SK;
-    if ((SK & 3) == 0) {
-      // four entries per thread, 16-byte stores into every rank's gather table
-      for (int q = blockIdx.x * blockDim.x + threadIdx.x; q < SK / 4; q += a.route_blocks * blockDim.x) {
-        const int4 e4 = reinterpret_cast<const int4*>(a.topk_own)[q];
-        const int4 w4 = reinterpret_cast<const int4*>(wbits)[q];
-        int4 p4;
-        p4.x = single_replica_slot(a, slots, e4.x);
-        p4.y = single_replica_slot(a, slots, e4.y);
-        p4.z = single_replica_slot(a, slots, e4.z);
-        p4.w = single_replica_slot(a, slots, e4.w);
-        reinterpret_cast<int4*>(a.phys_own)[q] = p4;
-        if (a.send_row) {
-          reinterpret_cast<int4*>(a.send_row)[q] = p4;
-          reinterpret_cast<int4*>(a.send_row + SK)[q] = w4;
-        }
-        for (int p = 0; p < a.world; ++p) {
-          int* row = reinterpret_cast<int*>(dst.ptr[p]) + row_off;
-          reinterpret_cast<int4*>(row)[q] = p4;
-          reinterpret_cast<int4*>(row + SK)[q] = w4;
-        }
-      }
-    } else {
-      for (int n = blockIdx.x * blockDim.x + threadIdx.x; n < SK; n += a.route_blocks * blockDim.x) {
-        const int p0 = single_replica_slot(a, slots, a.topk_own[n]);
-        const int wb = wbits[n];
-        a.phys_own[n] = p0;
-        if (a.send_row) { a.send_row[n] = p0; a.send_row[SK + n] = wb; }
-        for (int p = 0; p < a.world; ++p) {
-          int* row = reinterpret_cast<int*>(dst.ptr[p]) + row_off;
-          row[n] = p0;
-          row[SK + n] = wb;
-        }
-      }
-    }
   }
   // one fence per block (thread 0, after the block barrier) orders every thread's stores before the
   // block's arrival; the last block to arrive publishes the epoch words

@@ -14,6 +14,7 @@
 
 #include "../../include/zepp_b200.h"
 #include "common.cuh"
+#include "front.cuh"
 #include "gemm.cuh"
 #include "layer_kernels.cuh"
 #include "meta.cuh"
@@ -44,9 +45,14 @@ static int fail(const char* fmt, ...) {
   } while (0)
 
 static int swap_decide_prepare();
+static SwapArgs swap_args(const int* loads, int* p2l, int* l2p, const int* lcnts, int R, int G, int L, int nlp, double C,
+                          int cap, int max_rounds, long long* out);
+static size_t swap_smem(int R, int G, int L, int nlp);
 static size_t meta_smem(int R, int NN, int E_virt);
 static size_t pass2_smem(int tokens_per_tile, int K, int E_virt);
 static int pass2_prepare(size_t bytes);
+static int meta_fused_prepare(zepp_layer* l);
+static int front_push_blocks(const zepp_layer* l, int n_route);
 
 extern "C" const char* zepp_last_error(void) { return g_err.c_str(); }
 extern "C" int zepp_abi_version(void) { return 1; }
@@ -200,6 +206,8 @@ struct zepp_layer {
   zepp_rt* rt = nullptr;
   zepp_layer_cfg cfg{};
   int G, K, H, I, ffn1, W, L, NN, S, SK, nlp, gpe, E_virt, cap, max_tiles, tokens_per_tile, tiles_per_src;
+  int S_max;                                  // tokens per rank the buffers were sized for (S: the current bucket)
+  bool meta_fused = false;                    // the metadata runs as one cooperative launch (grid fits the device)
   unsigned long long epoch = 0;
   int64_t launches = 0;
   bool have_weights = false, have_placement = false;
@@ -219,7 +227,7 @@ struct zepp_layer {
   int *vce, *splits, *scatter_index, *sps, *uc, *tile_hist, *tile_uc, *expert_base;
   float* probs_all;
   long long *demands, *dplan, *cplan, *swap_block, *gate, *ovr0, *ovr1, *stag;
-  int* sched;
+  int *sched, *redirect;
   int *n_tiles, *tile_group, *tile_row0, *tile_rows, *m_this, *row_tok;
   unsigned int *tile_ready, *counters;
   long long* row_dst;
@@ -246,16 +254,16 @@ struct zepp_layer {
   unsigned long long* step_ctr = nullptr;     // device-resident step counter (epoch of the running step)
   int c_max = 1;                              // largest replica count of the resident placement
   bool use_graphs = true;
-  bool combine_lines = false;                 // combine epilogue writes staged 128-byte lines (ZEPP_B200_COMBINE_STAGED=1)
+  bool combine_lines = false;                 // combine epilogue writes staged 128-byte lines
   const void* fuse_x = nullptr;       // x of a whole-step call, published by the routing kernel
   const void* x_fused = nullptr;
   cudaStream_t capture_stream = nullptr;
-  // ZEPP_B200_PUSH_FORK=1: the dispatch push runs on a branch of the step beside the metadata kernels
-  bool push_fork = false;
-  cudaStream_t push_stream = nullptr;
-  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+  // whole-step calls: roles the front kernel takes over from their stand-alone kernels (set per enqueue)
+  bool front_route = false, front_push = false;
+  int front_blocks_max = 0;                   // blocks of the front kernel the device keeps resident at once
   struct StepGraph {
     const void *ids, *wts, *x, *y;
+    int tokens;                              // the bucket the launches were recorded for
     cudaGraphExec_t exec;
     int64_t kernels;
   };
@@ -278,7 +286,7 @@ extern "C" size_t zepp_layer_arena_bytes(const zepp_layer_cfg* c) {
   b += 3 * al(R * SK * 4) + al(E * 4) + al(R * E * 4) + al(R * (2 * R) * 4);
   b += al(R * tiles * E * 4) + al(R * tiles * 2 * R * 4) + al((E + 1) * 4);
   b += al(64 * 8) * 4 + al((size_t)zepp_swap_decide_out_ints((int)R, (int)G, (int)nlp, 8) * 8);
-  b += 8 * al(gpe * 8);
+  b += 9 * al(gpe * 8);
   b += 5 * al((gpe + cap / 128 + 8) * 4) + 3 * al(cap * 8) + al(cap * 4);
   b += 16 * al(R * 8) + (64 << 10);
   return b + (1 << 20);
@@ -340,6 +348,7 @@ static int layer_alloc(zepp_layer* l) {
   LA(l->swap_block, zepp_swap_decide_out_ints(R, l->G, l->nlp, 8));
   LA(l->gate, 2 * l->gpe);
   LA(l->sched, l->gpe);
+  LA(l->redirect, l->gpe);
   LA(l->ovr0, l->gpe);
   LA(l->ovr1, l->gpe);
   LA(l->stag, 16);
@@ -384,6 +393,7 @@ extern "C" int zepp_layer_create(zepp_rt* rt, const zepp_layer_cfg* c, zepp_laye
   l->G = c->num_experts; l->K = c->topk; l->H = c->hidden; l->I = c->ffn_hidden;
   l->ffn1 = c->act == 1 ? 2 * l->I : l->I;
   l->W = c->ranks; l->L = c->ranks_per_node; l->NN = l->W / l->L; l->S = c->max_tokens_per_rank;
+  l->S_max = l->S;
   l->SK = l->S * l->K;
   l->nlp = l->G / l->W + c->redundant_slots_per_rank;
   l->gpe = l->nlp + 1;
@@ -445,24 +455,16 @@ extern "C" int zepp_layer_create(zepp_rt* rt, const zepp_layer_cfg* c, zepp_laye
   CU_OK(cudaFuncSetAttribute(moe_gemm_kernel<MODE_DOWN_COMBINE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              GemmCfg<MODE_DOWN_COMBINE>::kSmemBytes));
   if (pass2_prepare(pass2_smem(l->tokens_per_tile, l->K, l->E_virt))) { delete l; return 1; }
+  if (meta_fused_prepare(l)) { delete l; return 1; }
   if (l->cfg.swap && swap_decide_prepare()) { delete l; return 1; }
   {
     const char* g = getenv("ZEPP_B200_GRAPHS");     // "0": launch the step's kernels one by one instead of as a graph
     if (g != nullptr && g[0] == '0') l->use_graphs = false;
-    // "1": the combine GEMM's epilogue stages rows in shared memory and stores whole 128-byte lines (for panels
-    // on peer GPUs).  Off unless asked for: this variant has not had its parity run on a GPU yet.
-    // "1": the staged dispatch push leaves the step's main line after the routing kernel and rejoins it before the
-    // reduce, so it overlaps the metadata kernels and the start of the dispatch GEMM.  Off unless asked for: an
-    // earlier form of it slowed the metadata kernels on the small shape and it has not been re-measured.
-    const char* pf = getenv("ZEPP_B200_PUSH_FORK");
-    if (pf != nullptr && pf[0] == '1' && l->stage != nullptr) {
-      CU_OK(cudaStreamCreateWithFlags(&l->push_stream, cudaStreamNonBlocking));
-      CU_OK(cudaEventCreateWithFlags(&l->ev_fork, cudaEventDisableTiming));
-      CU_OK(cudaEventCreateWithFlags(&l->ev_join, cudaEventDisableTiming));
-      l->push_fork = true;
-    }
+    // The combine GEMM's epilogue stages rows in shared memory and stores whole 128-byte lines when its rows go
+    // to panels on other ranks; "1" / "0" force that form on / off.
     const char* cs = getenv("ZEPP_B200_COMBINE_STAGED");
-    if (cs != nullptr && cs[0] == '1') l->combine_lines = true;
+    l->combine_lines = l->W > 1;
+    if (cs != nullptr && (cs[0] == '0' || cs[0] == '1')) l->combine_lines = cs[0] == '1';
   }
   if (meta_smem(l->W, l->NN, l->E_virt) > 48 * 1024) { delete l; return fail("too many ranks / experts for the metadata kernels"); }
   *out = l;
@@ -475,9 +477,6 @@ extern "C" int zepp_layer_destroy(zepp_layer* l) {
     cudaDeviceSynchronize();
     for (auto& gph : l->graphs) cudaGraphExecDestroy(gph.exec);
     if (l->capture_stream) cudaStreamDestroy(l->capture_stream);
-    if (l->push_stream) cudaStreamDestroy(l->push_stream);
-    if (l->ev_fork) cudaEventDestroy(l->ev_fork);
-    if (l->ev_join) cudaEventDestroy(l->ev_join);
     delete l;
   }
   return 0;
@@ -498,6 +497,15 @@ extern "C" int zepp_layer_set_placement(zepp_layer* l, const int32_t* p2l, const
   l->graphs.clear();
   l->have_placement = true;
   return 0;
+}
+
+extern "C" int zepp_layer_set_tokens(zepp_layer* l, int tokens) {
+  if (tokens < 1 || tokens > l->S_max) return fail("set_tokens: %d is outside 1..%d (max_tokens_per_rank)", tokens, l->S_max);
+  CU_OK(cudaSetDevice(l->rt->device));
+  l->S = tokens;
+  l->SK = tokens * l->K;
+  l->tiles_per_src = (tokens + l->tokens_per_tile - 1) / l->tokens_per_tile;
+  return meta_fused_prepare(l);
 }
 
 extern "C" int zepp_layer_weight_slots(zepp_layer* l, void** w1, void** w2) {
@@ -557,6 +565,7 @@ static MetaArgs layer_meta_args(zepp_layer* l) {
   m.routing_flags = l->W > 1 ? l->routing_flags : nullptr;
   m.epoch_ptr = l->step_ctr; m.limit_ns = l->rt->wait_ns; m.status = l->status;
   m.block_counter = l->counters + 8;
+  m.grid_sync = l->counters + 14;
   if (local_route(l)) {
     m.local_topk = l->ids_in; m.local_probs = l->wts_in; m.slot_of = l->slot_of; m.G = l->G;
     m.phys_own = l->phys_own; m.send_row = l->send_row;
@@ -569,22 +578,51 @@ static size_t meta_smem(int R, int NN, int E_virt) {
   const size_t a = (size_t)(E_virt + R + NN), b = meta_scan_smem_ints(R, NN, E_virt);   // pass1 counters / the scan
   return (a > b ? a : b) * sizeof(int);
 }
+static size_t fused_smem(const zepp_layer* l) {
+  return meta_fused_smem_ints(l->W, l->NN, l->E_virt, l->tokens_per_tile, l->K) * sizeof(int);
+}
+// Push blocks a front launch can add beside its metadata and route blocks (0: the push stays a kernel of its own).
+static int front_push_blocks(const zepp_layer* l, int n_route) {
+  int n = l->front_blocks_max - (l->W * l->tiles_per_src + 1) - n_route;
+  if (n > 128) n = 128;
+  if (n < 1 || (l->S + n - 1) / n > kPushMaxTokensPerBlock) return 0;
+  return n;
+}
+// Can the metadata of the current bucket run as one cooperative launch (every block resident at once)?
+static int meta_fused_prepare(zepp_layer* l) {
+  l->meta_fused = false;
+  const size_t bytes = fused_smem(l);
+  if (bytes > 200 * 1024) return 0;
+  const char* off = getenv("ZEPP_B200_META_FUSED");
+  if (off != nullptr && off[0] == '0') return 0;
+  if (bytes > 48 * 1024)
+    CU_OK(cudaFuncSetAttribute(meta_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+  int per_sm = 0;
+  CU_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, meta_fused_kernel, kMetaThreads, bytes));
+  l->front_blocks_max = per_sm * l->rt->sm_count;
+  l->meta_fused = l->front_blocks_max >= l->W * l->tiles_per_src + 1;
+  return 0;
+}
 static size_t pass2_smem(int tokens_per_tile, int K, int E_virt) {
   return (size_t)((tokens_per_tile * K + 31) / 32) * E_virt * sizeof(int);
 }
+// Kernel attributes belong to a device's instance of a function: remembered per device ordinal.
+constexpr int kMaxDevices = 64;
+static std::mutex g_attr_mutex;
+static size_t g_pass2_granted[kMaxDevices] = {};
+static bool g_swap_attr[kMaxDevices] = {};
+
 static int pass2_prepare(size_t bytes) {
-  static size_t granted = 48 * 1024;
   if (bytes > 200 * 1024) return fail("metadata: %zu bytes of shared memory per tile exceed the SM", bytes);
-  if (bytes > granted) {
+  if (bytes <= 48 * 1024) return 0;
+  int dev = -1;
+  CU_OK(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(g_attr_mutex);
+  if (dev < 0 || dev >= kMaxDevices || bytes > g_pass2_granted[dev]) {
     CU_OK(cudaFuncSetAttribute(meta_pass2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
-    granted = bytes;
+    if (dev >= 0 && dev < kMaxDevices) g_pass2_granted[dev] = bytes;
   }
   return 0;
-}
-
-__global__ void flags_wait_kernel(const unsigned long long* flags, int world, const unsigned long long* epoch_ptr,
-                                  unsigned long long limit_ns, unsigned long long* status, int what) {
-  block_wait_all(flags, world, step_epoch(epoch_ptr, false), limit_ns, status, what);
 }
 
 static SwapMoveArgs layer_swap_args(zepp_layer* l) {
@@ -600,6 +638,25 @@ static SwapMoveArgs layer_swap_args(zepp_layer* l) {
 // Does this step need the gathered loads?  Only the water-fill (some expert has more than one
 // replica) and the swap decision consume them.
 static bool needs_loads(const zepp_layer* l) { return l->c_max > 1 || l->cfg.swap != 0; }
+
+static SimpleRouteArgs layer_simple_route_args(zepp_layer* l) {
+  SimpleRouteArgs sa{};
+  const int R = l->W;
+  sa.topk_own = l->ids_in; sa.probs_own = l->wts_in; sa.slot_of = l->slot_of;
+  sa.SK = l->SK; sa.G = l->G; sa.R = R; sa.my_rank = l->rt->rank; sa.world = R; sa.first = needs_loads(l) ? 0 : 1;
+  sa.phys_own = l->phys_own; sa.send_row = l->send_row; sa.dst = l->xchg_dst[0]; sa.dst_odd = l->xchg_dst[1];
+  sa.flags = l->routing_flag_dst; sa.ctr = l->step_ctr; sa.block_counter = l->counters + 0; sa.status = l->status;
+  return sa;
+}
+
+static PushArgs layer_push_args(zepp_layer* l, const void* x) {
+  PushArgs pa{};
+  pa.phys_own = l->phys_own; pa.x = (const __nv_bfloat16*)x; pa.stage = l->stage_dst; pa.flags = l->push_flag_dst;
+  pa.S = l->S; pa.K = l->K; pa.H = l->H; pa.nlp = l->nlp; pa.rank = l->rt->rank; pa.world = l->W;
+  pa.region_tokens = l->S_max; pa.G = l->G;
+  pa.epoch_ptr = l->step_ctr; pa.counter = l->counters + 10; pa.status = l->status;
+  return pa;
+}
 
 extern "C" int zepp_layer_prepare_phase(zepp_layer* l, int phase, const int32_t* ids, const float* wts, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
@@ -620,19 +677,15 @@ extern "C" int zepp_layer_prepare_phase(zepp_layer* l, int phase, const int32_t*
   }
   if (phase == 1) {
     if (!l->cfg.swap) return 0;
-    // swap: decision on the gathered loads (rewrites p2l / l2p on the device), lane metadata, and the
-    // pull of this rank's incoming experts into staging; nothing is read on the host
-    const double C = (double)l->cfg.c_num / (double)l->cfg.c_den;
-    flags_wait_kernel<<<1, 64, 0, st>>>(R > 1 ? l->loads_flags : nullptr, R, l->step_ctr, l->rt->wait_ns, l->status, WAIT_LOADS);
-    LAUNCH_OK();
-    const int b = (int)(l->epoch & 1);
-    if (zepp_swap_decide(l->loads_all[b], l->p2l, l->l2p, l->lcnts, R, l->G, l->L, l->nlp, C, 8, 32,
-                         (int64_t*)l->swap_block, stream))
-      return 1;
-    l->launches++;
-    CU_OK(cudaMemsetAsync(l->sched, 0, l->gpe * 4, st));
-    lane_arm_kernel<<<1, 32, 0, st>>>(l->swap_block, R, me, l->nlp, 8, l->gate, l->sched, l->ovr0, l->ovr1, l->stag, 0,
-                                      l->step_ctr);
+    // swap: one launch waits for the gathered loads, decides (rewrites p2l / l2p on the device), rebuilds the
+    // router's slot table and marks this rank's incoming slots; then the pull of the incoming experts into
+    // staging.  Nothing is read on the host.
+    SwapArgs sa = swap_args(l->loads_all[0], l->p2l, l->l2p, l->lcnts, R, l->G, l->L, l->nlp,
+                            (double)l->cfg.c_num / (double)l->cfg.c_den, 8, 32, l->swap_block);
+    sa.loads_odd = l->loads_all[1]; sa.epoch_ptr = l->step_ctr; sa.loads_flags = R > 1 ? l->loads_flags : nullptr;
+    sa.limit_ns = l->rt->wait_ns; sa.status = l->status; sa.slot_of = l->slot_of; sa.rank = me;
+    sa.sched = l->sched; sa.redirect = l->redirect;
+    swap_decide_kernel<<<1, kSwapThreads, swap_smem(R, l->G, l->L, l->nlp), st>>>(sa);
     LAUNCH_OK();
     SwapMoveArgs sm = layer_swap_args(l);
     swap_pull_kernel<<<l->rt->sm_count * 2, 256, 0, st>>>(sm);
@@ -645,16 +698,11 @@ extern "C" int zepp_layer_prepare_phase(zepp_layer* l, int phase, const int32_t*
       SwapMoveArgs sm = layer_swap_args(l);
       swap_commit_kernel<<<l->rt->sm_count * 2, 256, 0, st>>>(sm);
       LAUNCH_OK();
-      slot_table_kernel<<<(l->G + 127) / 128, 128, 0, st>>>(l->l2p, l->lcnts, l->G, l->W, l->slot_of);
-      LAUNCH_OK();
     }
     if (local_route(l)) return 0;        // done by the first metadata kernel
+    if (l->c_max <= 1 && l->front_route) return 0;      // the front kernel's route blocks do it
     if (l->c_max <= 1) {
-      SimpleRouteArgs sa{};
-      sa.topk_own = l->ids_in; sa.probs_own = l->wts_in; sa.slot_of = l->slot_of;
-      sa.SK = l->SK; sa.G = l->G; sa.R = R; sa.my_rank = me; sa.world = R; sa.first = needs_loads(l) ? 0 : 1;
-      sa.phys_own = l->phys_own; sa.send_row = l->send_row; sa.dst = l->xchg_dst[0]; sa.dst_odd = l->xchg_dst[1];
-      sa.flags = l->routing_flag_dst; sa.ctr = l->step_ctr; sa.block_counter = l->counters + 0; sa.status = l->status;
+      SimpleRouteArgs sa = layer_simple_route_args(l);
       sa.route_blocks = (l->SK / 4 + 255) / 256 > 0 ? (l->SK / 4 + 255) / 256 : 1;
       if ((l->SK & 3) != 0) sa.route_blocks = (l->SK + 255) / 256;
       int grid = sa.route_blocks;
@@ -696,6 +744,25 @@ extern "C" int zepp_layer_prepare_phase(zepp_layer* l, int phase, const int32_t*
   if (phase == 3) {
     MetaArgs m = layer_meta_args(l);
     const int grid = R * l->tiles_per_src;
+    if (l->meta_fused) {
+      FrontArgs f{};
+      if (l->front_route) {
+        f.route = layer_simple_route_args(l);
+        f.n_route = ((l->SK + 3) / 4 + kMetaThreads - 1) / kMetaThreads;
+        f.first = f.route.first;
+        f.route_counter = l->counters + 0;
+      }
+      if (l->front_push) {
+        f.push = layer_push_args(l, l->fuse_x);
+        if (l->front_route) { f.push.phys_own = nullptr; f.push.topk_own = l->ids_in; f.push.slot_of = l->slot_of; }
+        f.n_push = front_push_blocks(l, f.n_route);
+      }
+      void* args[] = {(void*)&m, (void*)&f};
+      CU_OK(cudaLaunchCooperativeKernel((const void*)meta_fused_kernel, dim3(grid + 1 + f.n_route + f.n_push),
+                                        dim3(kMetaThreads), args, fused_smem(l), st));
+      l->launches++;
+      return 0;
+    }
     meta_pass1_kernel<<<grid, kMetaThreads, meta_smem(R, l->NN, l->E_virt), st>>>(m);      // + scan in its last block
     LAUNCH_OK();
     meta_pass2_kernel<<<grid, kMetaThreads, pass2_smem(l->tokens_per_tile, l->K, l->E_virt), st>>>(m);
@@ -731,7 +798,7 @@ static GemmArgs layer_gemm_args(zepp_layer* l, bool first) {
     g.x_ptrs = l->stage_ptrs; g.x_ptrs_odd = l->stage_ptrs; g.x_self = nullptr; g.x_flags = l->push_flags;
   }
   g.recv = l->recv; g.tile_ready = l->tile_ready; g.tokens_per_rank = l->S; g.gather = 0;
-  g.status = l->status; g.mbar_limit = 1u << 24; g.flag_limit_ns = l->rt->wait_ns;
+  g.status = l->status; g.mbar_limit_ns = 2 * l->rt->wait_ns + 1000000000ull; g.flag_limit_ns = l->rt->wait_ns;
   return g;
 }
 
@@ -777,10 +844,8 @@ extern "C" int zepp_layer_forward_phase(zepp_layer* l, int phase, const void* x,
       return 0;
     }
     if (l->stage != nullptr) {
-      PushArgs pa{};
-      pa.phys_own = l->phys_own; pa.x = (const __nv_bfloat16*)x; pa.stage = l->stage_dst; pa.flags = l->push_flag_dst;
-      pa.S = l->S; pa.K = l->K; pa.H = l->H; pa.nlp = l->nlp; pa.rank = l->rt->rank; pa.world = l->W;
-      pa.epoch_ptr = l->step_ctr; pa.counter = l->counters + 10; pa.status = l->status;
+      if (l->front_push) return 0;               // pushed by the front kernel of this step
+      PushArgs pa = layer_push_args(l, x);
       int grid = 2 * l->rt->sm_count;
       if (grid > l->S) grid = l->S;
       if (grid * 64 < l->S) grid = (l->S + 63) / 64;
@@ -847,33 +912,26 @@ extern "C" int zepp_layer_forward(zepp_layer* l, const void* x, void* y, void* s
 // One whole step in launch order.  x is published right after the first planning kernel, long before
 // the dispatch GEMM of any rank needs it, so the GEMM's wait for x never stalls on rank skew.
 static int step_enqueue(zepp_layer* l, const int32_t* ids, const float* wts, const void* x, void* y, void* stream) {
-  l->fuse_x = (!needs_loads(l) && l->c_max <= 1 && l->stage == nullptr) ? x : nullptr;
+  l->ids_in = ids;
+  l->wts_in = wts;
+  // roles the front kernel takes over in a whole-step call (x is known before the planning starts)
+  const bool staged = l->stage != nullptr;
+  const int n_route_blocks = ((l->SK + 3) / 4 + kMetaThreads - 1) / kMetaThreads;
+  l->front_route = staged && l->meta_fused && l->c_max <= 1 &&
+                   l->front_blocks_max >= l->W * l->tiles_per_src + 1 + n_route_blocks;
+  l->front_push = staged && l->meta_fused && front_push_blocks(l, l->front_route ? n_route_blocks : 0) > 0;
+  l->fuse_x = (l->front_push || (!needs_loads(l) && l->c_max <= 1 && !staged)) ? x : nullptr;
   l->x_fused = nullptr;
-  if (zepp_layer_prepare_phase(l, 0, ids, wts, stream)) return 1;
-  if (zepp_layer_prepare_phase(l, 1, ids, wts, stream)) return 1;
-  if (needs_loads(l) && l->stage == nullptr) {
-    if (zepp_layer_forward_phase(l, 0, x, y, stream)) return 1;
-    if (zepp_layer_prepare_phase(l, 2, ids, wts, stream)) return 1;
-  } else {
-    if (zepp_layer_prepare_phase(l, 2, ids, wts, stream)) return 1;     // commits the step counter
-    if (l->push_fork) {
-      // branch: push (reads only this rank's routing and x, writes the peers' staging) beside what follows
-      CU_OK(cudaEventRecord(l->ev_fork, (cudaStream_t)stream));
-      CU_OK(cudaStreamWaitEvent(l->push_stream, l->ev_fork, 0));
-      if (zepp_layer_forward_phase(l, 0, x, y, (void*)l->push_stream)) return 1;
-      CU_OK(cudaEventRecord(l->ev_join, l->push_stream));
-    } else {
-      if (zepp_layer_forward_phase(l, 0, x, y, stream)) return 1;
-    }
-  }
-  if (zepp_layer_prepare_phase(l, 3, ids, wts, stream)) return 1;
+  int rc = 0;
+  for (int ph = 0; ph < 3 && !rc; ++ph) rc = zepp_layer_prepare_phase(l, ph, ids, wts, stream);
+  // unfused dispatch with a loads exchange: publish x before the metadata so that no rank's pull waits for it
+  if (!rc && !staged && l->x_fused == nullptr) rc = zepp_layer_forward_phase(l, 0, x, y, stream);
+  if (!rc) rc = zepp_layer_prepare_phase(l, 3, ids, wts, stream);
+  if (!rc && staged) rc = zepp_layer_forward_phase(l, 0, x, y, stream);      // no-op when the front kernel pushed
+  for (int ph = 1; ph < 4 && !rc; ++ph) rc = zepp_layer_forward_phase(l, ph, x, y, stream);
   l->fuse_x = nullptr;
-  for (int ph = 1; ph < 4; ++ph) {
-    // the branch rejoins before the step's last kernel (the next step's push follows this step in order)
-    if (ph == 3 && l->push_fork) CU_OK(cudaStreamWaitEvent((cudaStream_t)stream, l->ev_join, 0));
-    if (zepp_layer_forward_phase(l, ph, x, y, stream)) return 1;
-  }
-  return 0;
+  l->front_route = l->front_push = false;
+  return rc;
 }
 
 // prepare + forward as one call.  The launch sequence of a step depends only on the four
@@ -886,7 +944,7 @@ extern "C" int zepp_layer_step(zepp_layer* l, const int32_t* ids, const float* w
   if (!l->have_weights) return fail("step: no weights set");
   if (!l->use_graphs) return step_enqueue(l, ids, wts, x, y, stream);
   for (auto& gph : l->graphs) {
-    if (gph.ids == ids && gph.wts == wts && gph.x == x && gph.y == y) {
+    if (gph.ids == ids && gph.wts == wts && gph.x == x && gph.y == y && gph.tokens == l->S) {
       CU_OK(cudaGraphLaunch(gph.exec, st));
       l->epoch += 1;
       l->launches += gph.kernels;
@@ -894,7 +952,7 @@ extern "C" int zepp_layer_step(zepp_layer* l, const int32_t* ids, const float* w
       return 0;
     }
   }
-  if (l->graphs.size() >= 32) return step_enqueue(l, ids, wts, x, y, stream);
+  if (l->graphs.size() >= 128) return step_enqueue(l, ids, wts, x, y, stream);
   const int64_t before = l->launches;
   const unsigned long long epoch_before = l->epoch;
   cudaGraph_t graph = nullptr;
@@ -918,7 +976,7 @@ extern "C" int zepp_layer_step(zepp_layer* l, const int32_t* ids, const float* w
     return step_enqueue(l, ids, wts, x, y, stream);
   }
   zepp_layer::StepGraph gph{};
-  gph.ids = ids; gph.wts = wts; gph.x = x; gph.y = y; gph.kernels = kernels;
+  gph.ids = ids; gph.wts = wts; gph.x = x; gph.y = y; gph.tokens = l->S; gph.kernels = kernels;
   e = cudaGraphInstantiate(&gph.exec, graph, 0);
   cudaGraphDestroy(graph);
   if (e != cudaSuccess) {
@@ -1038,12 +1096,7 @@ extern "C" int zepp_route(const int32_t* topk_own, int S, int K, const int32_t* 
     CU_OK(cudaGetLastError());
   }
   if (send_row != nullptr && probs_own != nullptr) {
-    static unsigned int* counter = nullptr;      // one word, lives for the process
-    if (!counter) {
-      CU_OK(cudaMalloc(&counter, 64));
-      CU_OK(cudaMemset(counter, 0, 64));
-    }
-    fa.block_counter = counter;
+    fa.block_counter = nullptr;                  // one block: it is its own last block
     route_finish_kernel<<<1, 256, 0, st>>>(fa);
     CU_OK(cudaGetLastError());
   }
@@ -1090,14 +1143,32 @@ extern "C" int zepp_routed_meta(const int32_t* gathered, const int32_t* vce_in, 
   m.expert_base = (int*)w;
   m.n_tiles = nullptr; m.row_tok = nullptr; m.status = nullptr; m.routing_flags = nullptr; m.epoch_ptr = nullptr;
   uint8_t* wend = (uint8_t*)m.expert_base + al((size_t)(E_virt + 1) * 4);
-  m.block_counter = (unsigned int*)wend;          // one self-resetting word at the end of the workspace
+  m.block_counter = (unsigned int*)wend;          // self-resetting arrival words at the end of the workspace
+  m.grid_sync = (unsigned int*)wend + 2;
   const int grid = (int)tiles;
   const size_t sm = meta_smem(R, NN, E_virt);
   const size_t sm2 = pass2_smem(m.tokens_per_tile, K, E_virt);
   if (gpe > kMetaThreads) return fail("routed_meta: too many groups per rank");
   if (sm > 48 * 1024) return fail("routed_meta: too many ranks / experts");
+  CU_OK(cudaMemsetAsync(m.block_counter, 0, 16, st));
+  // one cooperative launch when every block of it can be resident at once, else two launches
+  const size_t smf = meta_fused_smem_ints(R, NN, E_virt, m.tokens_per_tile, K) * sizeof(int);
+  const char* off = getenv("ZEPP_B200_META_FUSED");
+  if (smf <= 200 * 1024 && !(off != nullptr && off[0] == '0')) {
+    int per_sm = 0, dev = 0, sms = 0;
+    CU_OK(cudaGetDevice(&dev));
+    CU_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    if (smf > 48 * 1024)
+      CU_OK(cudaFuncSetAttribute(meta_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smf));
+    CU_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, meta_fused_kernel, kMetaThreads, smf));
+    if ((long long)per_sm * sms >= (long long)grid + 1) {
+      FrontArgs f{};
+      void* args[] = {(void*)&m, (void*)&f};
+      CU_OK(cudaLaunchCooperativeKernel((const void*)meta_fused_kernel, dim3(grid + 1), dim3(kMetaThreads), args, smf, st));
+      return 0;
+    }
+  }
   if (pass2_prepare(sm2)) return 1;
-  CU_OK(cudaMemsetAsync(m.block_counter, 0, 4, st));
   meta_pass1_kernel<<<grid, kMetaThreads, sm, st>>>(m);
   CU_OK(cudaGetLastError());
   meta_pass2_kernel<<<grid, kMetaThreads, sm2, st>>>(m);
@@ -1106,25 +1177,36 @@ extern "C" int zepp_routed_meta(const int32_t* gathered, const int32_t* vce_in, 
 }
 
 static int swap_decide_prepare() {
-  static bool attr = false;
-  if (!attr) {
+  int dev = -1;
+  CU_OK(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(g_attr_mutex);
+  if (dev < 0 || dev >= kMaxDevices || !g_swap_attr[dev]) {
     CU_OK(cudaFuncSetAttribute(swap_decide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    attr = true;
+    if (dev >= 0 && dev < kMaxDevices) g_swap_attr[dev] = true;
   }
   return 0;
 }
 
 extern "C" int zepp_swap_decide_out_ints(int R, int G, int nlp, int cap) { return 3 + R + 4 * R * cap + R * nlp + G; }
 
+static SwapArgs swap_args(const int* loads, int* p2l, int* l2p, const int* lcnts, int R, int G, int L, int nlp, double C,
+                          int cap, int max_rounds, long long* out) {
+  SwapArgs a{};
+  a.loads = loads; a.p2l = p2l; a.l2p = l2p; a.lcnts = lcnts; a.R = R; a.G = G; a.L = L; a.nlp = nlp; a.cap = cap;
+  a.max_rounds = max_rounds; a.C = C; a.out = out;
+  return a;
+}
+static size_t swap_smem(int R, int G, int L, int nlp) {
+  const int NS = R * nlp, NN = R / L, Q = NN * (L / 2) > 0 ? NN * (L / 2) : 1;
+  return (size_t)(G + NS + R) * 8 + (size_t)(2 * NS + 7 * Q + NN + (kSwapThreads / 32) * 16 + 8) * 4;
+}
+
 extern "C" int zepp_swap_decide(const int32_t* loads, int32_t* p2l, int32_t* l2p, const int32_t* lcnts, int R, int G,
                                 int L, int nlp, double C, int cap, int max_rounds, int64_t* out, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
   if (R % L || L > kSwapMaxL) return fail("swap_decide: bad topology R=%d L=%d", R, L);
-  SwapArgs a{};
-  a.loads = loads; a.p2l = p2l; a.l2p = l2p; a.lcnts = lcnts; a.R = R; a.G = G; a.L = L; a.nlp = nlp; a.cap = cap;
-  a.max_rounds = max_rounds; a.C = C; a.out = (long long*)out;
-  const int NS = R * nlp, NN = R / L, Q = NN * (L / 2) > 0 ? NN * (L / 2) : 1;
-  const size_t sm = (size_t)(G + NS + R) * 8 + (size_t)(2 * NS + 7 * Q + NN + (kSwapThreads / 32) * 16 + 8) * 4;
+  const SwapArgs a = swap_args(loads, p2l, l2p, lcnts, R, G, L, nlp, C, cap, max_rounds, (long long*)out);
+  const size_t sm = swap_smem(R, G, L, nlp);
   if (sm > 200 * 1024) return fail("swap_decide: tables too large for one block");
   if (swap_decide_prepare()) return 1;
   swap_decide_kernel<<<1, kSwapThreads, sm, st>>>(a);

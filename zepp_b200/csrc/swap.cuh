@@ -21,6 +21,16 @@ struct SwapArgs {
   int R, G, L, nlp, cap, max_rounds;
   double C;
   long long* out;       // [3 + R + 4*R*cap + R*nlp + G]
+  // ---- inside a layer step (all nullptr / 0 for the stand-alone entry point)
+  const int* loads_odd;                    // the loads table of odd epochs (picked on the device, like the router does)
+  const unsigned long long* epoch_ptr;     // device step counter
+  const unsigned long long* loads_flags;   // [R] arrival words of the loads exchange (waited for here), or nullptr
+  unsigned long long limit_ns;
+  unsigned long long* status;
+  int* slot_of;         // [G] out: the first valid l2p entry of every expert on the placement this step routes on
+  int rank;
+  int* sched;           // [gpe] out: schedule word per local group (bit 30 = slot received an expert this step)
+  int* redirect;        // [gpe] out: group whose weights the GEMMs read: the group itself, or gpe + i for the i-th incoming expert
 };
 
 __device__ __forceinline__ bool band_out(const long long* Lr, int n, int L, double C) {
@@ -40,6 +50,30 @@ __device__ __forceinline__ void slot_key(const int* cur, const long long* w, int
   else { k1 = kSwapBig; k2 = kSwapBig; }
 }
 
+// Tables the rest of a layer step reads, from the placement `cur` the decision left ([R*nlp] experts per slot):
+// slot_of (the router's slot lookup) and, for this rank, which groups received an expert (their tiles are
+// scheduled last and read their weights from the staging entries until the step's end).
+__device__ void swap_step_tables(const SwapArgs& a, const int* cur, int cnt, const long long* mv) {
+  const int NS = a.R * a.nlp, gpe = a.nlp + 1;
+  if (a.slot_of != nullptr) {
+    for (int e = threadIdx.x; e < a.G; e += blockDim.x) {
+      int p0 = -1;
+      for (int s = 0; s < NS && p0 < 0; ++s)
+        if (cur[s] == e) p0 = s;
+      a.slot_of[e] = p0;
+    }
+  }
+  if (a.sched != nullptr) {
+    for (int g = threadIdx.x; g < gpe; g += blockDim.x) {
+      int hit = -1;
+      for (int i = 0; i < cnt; ++i)
+        if ((int)mv[4 * i] == g - 1) hit = i;
+      a.sched[g] = hit >= 0 ? (1 << 30) : 0;
+      a.redirect[g] = hit >= 0 ? gpe + hit : g;
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kSwapThreads) swap_decide_kernel(SwapArgs a) {
   extern __shared__ long long sm64[];
   const int R = a.R, G = a.G, L = a.L, nlp = a.nlp, NS = R * nlp, NN = R / L, P = L / 2, Q = NN * P;
@@ -56,6 +90,11 @@ __global__ void __launch_bounds__(kSwapThreads) swap_decide_kernel(SwapArgs a) {
   __shared__ int s_any, s_stop, s_rounds;
   const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, wid = tid >> 5, nw = nt >> 5;
   const int off_cnt = 3, off_mv = 3 + R, off_p2l = off_mv + 4 * R * a.cap, off_lg = off_p2l + NS;
+  if (a.epoch_ptr != nullptr) {
+    const unsigned long long epoch = step_epoch(a.epoch_ptr, false);
+    if (epoch & 1) a.loads = a.loads_odd;
+    if (!block_wait_all(a.loads_flags, R, epoch, a.limit_ns, a.status, WAIT_LOADS)) return;
+  }
 
   for (int e = tid; e < G; e += nt) {
     long long s = 0;
@@ -220,6 +259,7 @@ __global__ void __launch_bounds__(kSwapThreads) swap_decide_kernel(SwapArgs a) {
     if (tid == 0) { a.out[0] = 0; a.out[1] = 0; a.out[2] = 0; }
     for (int r = tid; r < R; r += nt) a.out[off_cnt + r] = 0;
     for (int s = tid; s < NS; s += nt) a.out[off_p2l + s] = a0[s];
+    swap_step_tables(a, cur, 0, nullptr);
     return;
   }
   for (int s = tid; s < NS; s += nt) { a.out[off_p2l + s] = cur[s]; a.p2l[s] = cur[s]; }
@@ -254,6 +294,12 @@ __global__ void __launch_bounds__(kSwapThreads) swap_decide_kernel(SwapArgs a) {
   }
   __syncthreads();
   if (tid == 0) { a.out[0] = rounds; a.out[1] = s_total; a.out[2] = s_err; }
+  if (a.slot_of != nullptr || a.sched != nullptr) {
+    __threadfence_block();
+    __syncthreads();
+    const int cnt = a.sched != nullptr ? min((int)a.out[off_cnt + a.rank], a.cap) : 0;
+    swap_step_tables(a, cur, cnt, a.out + off_mv + (size_t)a.rank * a.cap * 4);
+  }
 }
 
 // Swap-lane metadata of one rank from the decision's result block: gate words of the unchanged

@@ -33,6 +33,17 @@ def activation(h, shape, out=None):
     return torch.mul(torch.nn.functional.silu(h[:, :ffn]), h[:, ffn:], out=out)
 
 
+def token_buckets(cfg):
+    """Token counts a layer captures a step for: k, 2k, 4k, ... and max_tokens_per_rank (all multiples of top-k),
+    as the reference's serving path pads to (python/zepp/serving.py:42-50)."""
+    k, top = cfg.shape.topk, cfg.max_tokens_per_rank
+    out, s = [], k
+    while s < top:
+        out.append(s)
+        s *= 2
+    return out + [top]
+
+
 class Marks:
     """Optional bracket marks for benchmarking (a callable per boundary)."""
 
@@ -98,6 +109,8 @@ class EPMoE(torch.nn.Module):
         self._swap_moves = 0
         self._epoch = 0
         self._plan_views = None
+        self._tokens = cfg.max_tokens_per_rank        # the bucket the next step runs at
+        self._pad_bufs = {}
 
     @staticmethod
     def arena_bytes(cfg, caps):
@@ -151,8 +164,41 @@ class EPMoE(torch.nn.Module):
     def _ids(self, topk_ids, topk_weights):
         ids = topk_ids.to(device=self.device, dtype=torch.int32).contiguous()
         wts = topk_weights.to(device=self.device, dtype=torch.float32).contiguous()
-        assert ids.shape == (self.cfg.max_tokens_per_rank, self.cfg.shape.topk), tuple(ids.shape)
+        assert ids.shape == (self._tokens, self.cfg.shape.topk), (tuple(ids.shape), self._tokens)
         return ids, wts
+
+    # -- token buckets ----------------------------------------------------------------------
+    def set_tokens(self, tokens):
+        """Run the following steps at `tokens` rows per rank (<= max_tokens_per_rank; every rank must choose the
+        same value, as the reference's ranks pad to a common bucket, python/zepp/serving.py:5-6).  Buffers keep
+        their size; a step graph is captured per (bucket, tensors)."""
+        tokens = int(tokens)
+        if tokens != self._tokens:
+            self._h.set_tokens(tokens)
+            self._tokens = tokens
+            self._plan_views = None
+
+    def step_padded(self, topk_ids, topk_weights, x, bucket=None):
+        """One step on n <= bucket real tokens: rows n..bucket-1 are pad rows (expert id -1: no owner, no transfer,
+        no compute, not counted in the loads).  `bucket` defaults to the smallest of token_buckets(cfg) that holds n;
+        every rank must pass the same bucket.  Returns y[:n].  The padded inputs live in per-bucket buffers, so a
+        bucket's step graph is captured once."""
+        n = int(topk_ids.shape[0])
+        if bucket is None:
+            bucket = next(b for b in token_buckets(self.cfg) if b >= n)
+        assert n <= bucket <= self.cfg.max_tokens_per_rank, (n, bucket)
+        K, H = self.cfg.shape.topk, self.cfg.shape.hidden
+        if bucket not in self._pad_bufs:
+            self._pad_bufs[bucket] = (torch.full((bucket, K), -1, dtype=torch.int32, device=self.device),
+                                      torch.zeros(bucket, K, dtype=torch.float32, device=self.device),
+                                      torch.zeros(bucket, H, dtype=self.dtype, device=self.device))
+        ids_b, w_b, x_b = self._pad_bufs[bucket]
+        ids_b[:n].copy_(topk_ids)
+        ids_b[n:].fill_(-1)
+        w_b[:n].copy_(topk_weights)
+        x_b[:n].copy_(x)
+        self.set_tokens(bucket)
+        return self.step(ids_b, w_b, x_b)[:n]
 
     def prepare(self, topk_ids, topk_weights, marks=None, phase=None):
         """Loads exchange -> (swap decision) -> route -> routing exchange -> metadata; returns the Plan.
@@ -181,30 +227,33 @@ class EPMoE(torch.nn.Module):
         return Plan(self._plan_views[0], self._plan_views[1], stable=True, epoch=self._epoch)
 
     def forward(self, x, plan=None, marks=None, phase=None):
-        assert x.shape == (self.cfg.max_tokens_per_rank, self.cfg.shape.hidden), tuple(x.shape)
+        assert x.shape == (self._tokens, self.cfg.shape.hidden), (tuple(x.shape), self._tokens)
         x = x.contiguous()
+        y = self._y[:self._tokens]
         if phase is not None:
-            self._h.forward(x, self._y, phase)
-            return self._y
+            self._h.forward(x, y, phase)
+            return y
         if marks is None:
-            self._h.forward(x, self._y)
-            return self._y
-        self._h.forward(x, self._y, 0)
-        self._h.forward(x, self._y, 1)
+            self._h.forward(x, y)
+            return y
+        self._h.forward(x, y, 0)
+        self._h.forward(x, y, 1)
         marks("dispatch")
         marks("act")                     # the activation runs in the dispatch GEMM's epilogue
-        self._h.forward(x, self._y, 2)
-        self._h.forward(x, self._y, 3)
+        self._h.forward(x, y, 2)
+        self._h.forward(x, y, 3)
         marks("combine")
-        return self._y
+        return y
 
     def step(self, topk_ids, topk_weights, x):
         """prepare + forward in one runtime call (lowest host overhead)."""
         ids, wts = self._ids(topk_ids, topk_weights)
         self._keep = (ids, wts)
-        self._h.step(ids, wts, x.contiguous(), self._y)
+        assert x.shape == (self._tokens, self.cfg.shape.hidden), (tuple(x.shape), self._tokens)
+        y = self._y[:self._tokens]
+        self._h.step(ids, wts, x.contiguous(), y)
         self._epoch += 1
-        return self._y
+        return y
 
     # -- verdict ----------------------------------------------------------------------------
     def check(self):
@@ -303,4 +352,4 @@ def local_step(layers, ids_all, wts_all, xs):
     for ph in range(4):
         for r, l in enumerate(layers):
             l.forward(xs[r], phase=ph)
-    return [l._y for l in layers]
+    return [l._y[:l._tokens] for l in layers]

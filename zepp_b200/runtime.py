@@ -101,6 +101,9 @@ class LayerHandle:
                                              l2p.ctypes.data_as(ctypes.c_void_p), lc.ctypes.data_as(ctypes.c_void_p),
                                              self._stream()))
 
+    def set_tokens(self, tokens):
+        check(lib().zepp_layer_set_tokens(self.h, int(tokens)))
+
     @staticmethod
     def _stream():
         return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)

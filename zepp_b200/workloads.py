@@ -76,6 +76,15 @@ def fast_weights(shape: ModelShape, experts, device, seed=7):
     return out
 
 
+def device_expert(e, shape: ModelShape, device, seed=7):
+    """N(0, 0.02) weights (w1 [ffn1, H], w2 [H, I], bf16) of expert e generated on `device`, a function of
+    (seed, e) only: any rank can regenerate any expert (benchmark set-up and its sampled parity check)."""
+    g = torch.Generator(device=device).manual_seed(seed * 100003 + e)
+    w1 = (0.02 * torch.randn(shape.ffn1, shape.hidden, generator=g, device=device)).bfloat16()
+    w2 = (0.02 * torch.randn(shape.hidden, shape.ffn_hidden, generator=g, device=device)).bfloat16()
+    return w1, w2
+
+
 def make(name, W, seed=0, S=None):
     """(shape, S, ids [W,S,K], wts [W,S,K], popularity, generator) of a named workload at W ranks."""
     key, S0, zipf_s, _c, _swap = WORKLOADS[name]
