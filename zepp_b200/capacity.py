@@ -31,16 +31,25 @@ def violations(d: Demands, c: Capacities, direct: bool = False):
 
 
 def grow(c: Capacities, d: Demands, factor: float = 1.5, direct: bool = False) -> Capacities:
-    new = {f.name: getattr(c, f.name) for f in fields(c)}
-    for df, cf in (_FIT_DIRECT if direct else _FIT):
-        new[cf] = max(new[cf], int(math.ceil(factor * getattr(d, df))))
-    new["combine_send"] = max(new["combine_send"], new["recv_cap"])
-    new["dispatch_recv"] = max(new["dispatch_recv"], new["recv_cap"])
-    return Capacities(**new)
+    """Capacities that hold `d` with headroom: every checked buffer becomes at least ceil(factor * demand) and never
+    shrinks; the two buffers that alias the receive rows follow recv_cap (growth rule of the reference,
+    python/zepp/capacity.py:75-82)."""
+    wanted = {}
+    for demand_field, cap_field in (_FIT_DIRECT if direct else _FIT):
+        need = math.ceil(factor * getattr(d, demand_field))
+        wanted[cap_field] = max(wanted.get(cap_field, 0), need)
+    values = {f.name: max(getattr(c, f.name), wanted.get(f.name, 0)) for f in fields(c)}
+    for follower in ("combine_send", "dispatch_recv"):
+        values[follower] = max(values[follower], values["recv_cap"])
+    return Capacities(**values)
 
 
 class CapacityExceeded(Exception):
+    """A step's exact demands do not fit the buffers; `.violations` lists (capacity, needed, held) and `.demands`
+    holds the step's Demands (what EPMoE.resize_capacities grows from)."""
+
     def __init__(self, viol, demands: Demands):
-        super().__init__("capacity exceeded: " + ", ".join(f"{f} needs {n} > {h}" for f, n, h in viol))
-        self.violations = viol
+        self.violations = list(viol)
         self.demands = demands
+        parts = [f"{name} needs {needed} > {held}" for name, needed, held in self.violations]
+        super().__init__("capacity exceeded: " + ", ".join(parts))

@@ -27,6 +27,8 @@ enum StatusWord : int {
   // cycle sums of a -DZEPP_GEMM_PROFILE build (not time stamps): MMA thread waiting for operand stages / for a free
   // accumulator, epilogue warp working / waiting
   TR_PROF_MMA_DATA = 26, TR_PROF_MMA_ACC = 27, TR_PROF_EPI_BUSY = 28, TR_PROF_EPI_WAIT = 29,
+  // the same four words in a normal build: stamps of the swap kernels that run before the routing
+  TR_LOADS = 26, TR_DECIDE = 27, TR_DECIDE_GO = 28, TR_DECIDE_END = 29,
   TR_GATHER_END = 30,  // dispatch GEMM: the last gather warp finished (max over warps)
   TR_FIRST_ITEMS = 31, // dispatch GEMM: latest start of a CTA's first item (max over CTAs)
   TR_RING = 32,        // start stamps of the last 16 steps (slot = epoch % 16), then their end stamps
@@ -41,7 +43,7 @@ enum ErrorBit : unsigned long long {
 enum WaitId : int {
   WAIT_LOADS = 1, WAIT_ROUTING = 2, WAIT_X = 3, WAIT_COMBINE = 4, WAIT_MBAR_FULL = 5,
   WAIT_MBAR_EMPTY = 6, WAIT_TMEM_FULL = 7, WAIT_TMEM_EMPTY = 8, WAIT_TILE_READY = 9,
-  WAIT_BARRIER = 10, WAIT_TEST = 11
+  WAIT_BARRIER = 10, WAIT_TEST = 11, WAIT_WEIGHTS = 12
 };
 
 __device__ __forceinline__ unsigned long long globaltimer_ns() {

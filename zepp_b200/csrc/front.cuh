@@ -72,6 +72,14 @@ __global__ void __launch_bounds__(kMetaThreads) meta_fused_kernel(MetaArgs a, co
         }
       }
     } else {
+      // The routing rows are small and every rank's metadata waits for them: the token rows (megabytes on the
+      // same links) follow them, so a push block starts once this rank's route blocks have raised their flag here.
+      if (f.n_route > 0 && threadIdx.x == 0) {
+        const unsigned long long* mine = reinterpret_cast<const unsigned long long*>(f.route.flags.ptr[f.route.my_rank]) + f.route.my_rank;
+        if (!wait_epoch_geq(mine, epoch, a.limit_ns != 0 ? a.limit_ns : 4000000000ull))
+          record_timeout(a.status, WAIT_ROUTING, f.route.my_rank, (long long)epoch);      // push anyway: the rows are still needed
+      }
+      __syncthreads();
       push_block(f.push, role - f.n_route, f.n_push, epoch);
     }
     return;

@@ -36,6 +36,7 @@ constexpr int kXTileBytes = kTileN * kTileK * 2;   // 16 KB
 constexpr int kAccStages = 2;
 constexpr int kMaxGatherWarps = 8;     // warps 6.. of a dispatch GEMM CTA in fused mode (4 or 8, chosen at launch)
 constexpr int kMaxTilesSmem = 1024;   // token tiles of one rank and step held in shared memory
+constexpr int kSwapChunkVecs = 2048;  // 16-byte vectors a mover warp copies per credit (32 KB)
 
 // -DZEPP_GEMM_PROFILE: CTA 0 of the dispatch GEMM sums, in SM cycles, how long its MMA thread waited for
 // operand stages and for a free accumulator, and how long an epilogue warp worked and waited for
@@ -85,6 +86,18 @@ struct GemmArgs {
   unsigned int* tile_ready;                // [max_tiles] rows landed per tile (zeroed per step)
   int tokens_per_rank;
   int gather;                              // 1: run the gather warps and gate tiles on tile_ready
+  // expert swap: this step's incoming experts (the decision's result block) are pulled from their source ranks'
+  // slots into the staging groups that follow the slot groups of the weight tensor by this kernel's spare warps,
+  // while the tiles of every other group compute; a tile of a staging group waits for its expert's chunks
+  // (replaces the weight lanes of python/zepp/swap.py:464-559 and src/planner/lane_device.cu:82-163, and their
+  // gate words polled by the GEMMs' tile loops)
+  const long long* swap_block;             // nullptr: no swap in this layer
+  int swap_ranks, swap_cap;                // R and moves per rank of the block's layout
+  int n_groups;                            // gpe: groups >= n_groups are staging entries
+  const uint4* const* w_peers;             // [W] peers' slot bases of this GEMM's weight matrix
+  uint4* w_slots;                          // this rank's base of the same tensor (slots, then staging)
+  unsigned long long w_vec;                // 16-byte vectors of one group
+  unsigned int* w_ready;                   // [cap] chunks landed per staging entry (zeroed by the decision kernel)
   // bounded waits
   unsigned long long* status;
   unsigned long long mbar_limit_ns;   // inner (mbarrier) waits enclose the cross-rank waits: bounded later than those
@@ -226,6 +239,26 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         const uint32_t x_bytes = (rows <= 32 ? 32u : (rows <= 64 ? 64u : 128u)) * (kTileK * 2);
         const uint32_t tx = (Cfg::kDual ? 2u : 1u) * kWTileBytes + x_bytes;
         const int w_row = grp * a.w_rows_per_group + j * Cfg::kFeatPerItem;
+        if (a.swap_block != nullptr && grp >= a.n_groups) {
+          // weights of an expert that arrives this step: wait for all of its chunks in the staging group
+          const unsigned int need = (unsigned int)((a.w_vec + kSwapChunkVecs - 1) / kSwapChunkVecs);
+          const unsigned int* cnt = a.w_ready + (grp - a.n_groups);
+          const unsigned long long t0 = globaltimer_ns();
+          bool ok = true;
+          while (ld_acquire_gpu_u32(cnt) < need) {
+            if (*abortp || globaltimer_ns() - t0 > a.flag_limit_ns) {
+              record_timeout(a.status, WAIT_WEIGHTS, grp - a.n_groups, (long long)epoch);
+              ok = false;
+              break;
+            }
+            __nanosleep(128);
+          }
+          if (!ok) {
+            abort_flag = 1;
+            break;
+          }
+          fence_proxy_async();        // the movers' generic-proxy stores -> TMA reads
+        }
         int kb_first = 0;
         if (MODE != MODE_DOWN_COMBINE && a.gather) {
           // rows of this tile are pulled by gather warps (of any CTA).  If they have not all landed yet,
@@ -588,6 +621,47 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
           }
         }
         if (lane == 0) trace_mark_max(a.status, TR_GATHER_END);
+      }
+    }
+    if (a.swap_block != nullptr && !*abortp) {
+      // ---------------------------------------------------------------- movers (incoming experts of a swap)
+      const long long rounds = a.swap_block[0];
+      int cnt = rounds > 0 ? (int)a.swap_block[3 + a.rank] : 0;
+      if (cnt > a.swap_cap) cnt = a.swap_cap;
+      if (cnt > 0) {
+        const long long* mv = a.swap_block + 3 + a.swap_ranks + (size_t)a.rank * a.swap_cap * 4;
+        const int spare = (int)(blockDim.x >> 5) - 6;
+        const unsigned long long n_warps = (unsigned long long)gridDim.x * spare;
+        const unsigned long long me = (unsigned long long)blockIdx.x * spare + (warp - 6);
+        const unsigned long long per = (a.w_vec + kSwapChunkVecs - 1) / kSwapChunkVecs;
+        for (unsigned long long c = me; c < per * cnt; c += n_warps) {
+          const int m = (int)(c / per);
+          const unsigned long long v_lo = (c - (unsigned long long)m * per) * kSwapChunkVecs;
+          const unsigned long long v_hi = v_lo + kSwapChunkVecs < a.w_vec ? v_lo + kSwapChunkVecs : a.w_vec;
+          const int src_rank = (int)mv[4 * m + 1], src_slot = (int)mv[4 * m + 2];
+          if (src_rank >= 0 && src_rank < a.world) {
+            const uint4* sp = a.w_peers[src_rank] + (unsigned long long)(1 + src_slot) * a.w_vec;
+            uint4* dp = a.w_slots + (unsigned long long)(a.n_groups + m) * a.w_vec;
+            for (unsigned long long v0 = v_lo; v0 < v_hi; v0 += 256) {
+              uint4 buf[8];
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                const unsigned long long v = v0 + q * 32 + lane;
+                if (v < v_hi) buf[q] = sp[v];
+              }
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                const unsigned long long v = v0 + q * 32 + lane;
+                if (v < v_hi) dp[v] = buf[q];
+              }
+            }
+          } else if (lane == 0 && a.status != nullptr) {
+            atomicOr(a.status + ST_ERROR, (unsigned long long)ERR_BAD_INDEX);
+          }
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) atomicAdd(a.w_ready + m, 1u);
+        }
       }
     }
   }

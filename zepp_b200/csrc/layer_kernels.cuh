@@ -5,6 +5,7 @@
 #pragma once
 #include "common.cuh"
 #include "planner.cuh"
+#include "swap.cuh"
 
 namespace zepp {
 
@@ -224,7 +225,7 @@ __global__ void combine_push_kernel(MoveArgs a) {
 __global__ void combine_reduce_kernel(const __nv_bfloat16* __restrict__ panel, __nv_bfloat16* __restrict__ y, int S,
                                       int K, int H, const unsigned long long* done_flags, int world,
                                       const unsigned long long* epoch_ptr, unsigned long long limit_ns,
-                                      unsigned long long* status) {
+                                      unsigned long long* status, const SwapCommitArgs commit) {
   const unsigned long long epoch = step_epoch(epoch_ptr, false);
   if (blockIdx.x == 0 && threadIdx.x == 0) trace_mark(status, TR_REDUCE);
   if (!block_wait_all(done_flags, world, epoch, limit_ns, status, WAIT_COMBINE)) return;
@@ -263,10 +264,11 @@ __global__ void combine_reduce_kernel(const __nv_bfloat16* __restrict__ panel, _
     for (int q = 0; q < 4; ++q) o2[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
     reinterpret_cast<uint4*>(y + t * H)[v] = out;
   }
-  if (threadIdx.x == 0) {
-    trace_mark_max(status, TR_REDUCE_END);
-    trace_mark_max(status, TR_RING + 16 + (int)(epoch & 15));
-  }
+  if (threadIdx.x == 0) trace_mark_max(status, TR_REDUCE_END);
+  // every rank's combine GEMM has finished (the wait above), so nobody reads this rank's old slot contents any more:
+  // the experts that arrived this step move from staging into their slots
+  swap_commit(commit);
+  if (threadIdx.x == 0) trace_mark_max(status, TR_RING + 16 + (int)(epoch & 15));
 }
 
 }  // namespace zepp

@@ -79,6 +79,7 @@ struct MetaArgs {
   int hidden;               // H (row_dst is an element offset into the home's [S*K, H] panel)
   int staged;               // 1: row_tok holds (source, staging slot) instead of (source, token)
   const int* group_order;   // [gpe] schedule word per group (bit 30 = moved-in slot: its tiles go last) or nullptr
+  const int* group_redirect;// [gpe] group whose weights a group's tiles read (a staging entry for a moved-in slot) or nullptr
   // exchange wait
   const unsigned long long* routing_flags;
   const unsigned long long* epoch_ptr;
@@ -383,7 +384,7 @@ __device__ void meta_scan_body(MetaArgs& a, int* sm, bool bases_in_place) {
     for (int t = 0; t < nt; ++t) {
       const int slot = first + t;
       if (slot < a.max_tiles) {
-        a.tile_group[slot] = e;
+        a.tile_group[slot] = a.group_redirect != nullptr ? a.group_redirect[e] : e;
         a.tile_row0[slot] = off + t * kTileRowsMax;
         a.tile_rows[slot] = min(kTileRowsMax, me - t * kTileRowsMax);
         a.tile_ready[slot] = 0u;

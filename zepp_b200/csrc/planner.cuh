@@ -61,6 +61,7 @@ __global__ void loads_publish_kernel(const int* __restrict__ topk_own, int n_ent
   extern __shared__ int hist[];
   const unsigned long long epoch = step_epoch(ctr, true);      // first kernel of a step
   const PeerTable& dst = (epoch & 1) ? dst1 : dst0;
+  if (threadIdx.x == 0) trace_mark(status, TR_LOADS);
   if (route_stats != nullptr && threadIdx.x < 4) route_stats[threadIdx.x] = 0;
   for (int g = threadIdx.x; g < G; g += blockDim.x) hist[g] = 0;
   __syncthreads();

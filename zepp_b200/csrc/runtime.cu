@@ -23,6 +23,8 @@
 
 using namespace zepp;
 
+constexpr int kSwapCap = 8;        // expert moves per rank and step (the reference's SWAP_MAX_MOVES)
+
 // ---------------------------------------------------------------------------------------------
 // errors
 // ---------------------------------------------------------------------------------------------
@@ -235,11 +237,10 @@ struct zepp_layer {
   unsigned long long* status;
   // device pointer tables
   const __nv_bfloat16** x_ptrs[2];
-  // swap: weight slots owned by the layer (peer-visible), staging for incoming experts, pulled flags
-  __nv_bfloat16 *w1_slots = nullptr, *w2_slots = nullptr, *stag1 = nullptr, *stag2 = nullptr;
-  unsigned long long* swap_flags = nullptr;
+  // swap: weight slots owned by the layer (peer-visible) with the staging groups of incoming experts behind them
+  __nv_bfloat16 *w1_slots = nullptr, *w2_slots = nullptr;     // [gpe + kSwapCap][...]
   const uint4 **w1_peers = nullptr, **w2_peers = nullptr;
-  PeerTable swap_flag_dst;
+  unsigned int* w_ready = nullptr;                            // [2 * kSwapCap] chunk counters of the staging entries
   const __nv_bfloat16** stage_ptrs = nullptr;   // [W] this rank's staging regions (one per source)
   PeerTable stage_dst, push_flag_dst;
   __nv_bfloat16** panels;
@@ -313,10 +314,9 @@ static int layer_alloc(zepp_layer* l) {
   for (int b = 0; b < 2; ++b) LA(l->xsym[b], (size_t)l->S * l->H);
   LA(l->panel, (size_t)l->SK * l->H);
   LA(l->push_flags, R);
-  LA(l->swap_flags, R);
   if (l->cfg.swap) {
-    LA(l->w1_slots, (size_t)l->gpe * l->ffn1 * l->H);
-    LA(l->w2_slots, (size_t)l->gpe * l->H * l->I);
+    LA(l->w1_slots, (size_t)(l->gpe + kSwapCap) * l->ffn1 * l->H);
+    LA(l->w2_slots, (size_t)(l->gpe + kSwapCap) * l->H * l->I);
   }
   if (R > 1 && l->cfg.strategy == 0) LA(l->stage, (size_t)R * l->S * l->H);
   // local part
@@ -367,8 +367,7 @@ static int layer_alloc(zepp_layer* l) {
   for (int b = 0; b < 2; ++b) LA(l->x_ptrs[b], R);
   LA(l->stage_ptrs, R);
   if (l->cfg.swap) {
-    LA(l->stag1, (size_t)8 * l->ffn1 * l->H);
-    LA(l->stag2, (size_t)8 * l->H * l->I);
+    LA(l->w_ready, 2 * kSwapCap);
     LA(l->w1_peers, R);
     LA(l->w2_peers, R);
   }
@@ -423,7 +422,6 @@ extern "C" int zepp_layer_create(zepp_rt* rt, const zepp_layer_cfg* c, zepp_laye
     l->routing_flag_dst.ptr[p] = peer_ptr(rt, p, l->routing_flags);
     l->x_flag_dst.ptr[p] = peer_ptr(rt, p, l->x_flags);
     l->push_flag_dst.ptr[p] = peer_ptr(rt, p, l->push_flags);
-    l->swap_flag_dst.ptr[p] = peer_ptr(rt, p, l->swap_flags);
     l->stage_dst.ptr[p] = l->stage ? (void*)peer_ptr(rt, p, l->stage) : nullptr;
     pp[p] = peer_ptr(rt, p, l->panel);
     dp[p] = peer_ptr(rt, p, l->done_flags);
@@ -524,8 +522,9 @@ extern "C" int zepp_layer_set_weights(zepp_layer* l, const void* w1, const void*
     w1 = l->w1_slots;
     w2 = l->w2_slots;
   }
-  if (make_map(&l->tm_w1, w1, (uint64_t)l->gpe * l->ffn1, l->H, 128)) return 1;
-  if (make_map(&l->tm_w2, w2, (uint64_t)l->gpe * l->H, l->I, 128)) return 1;
+  const uint64_t groups = l->gpe + (l->cfg.swap ? kSwapCap : 0);       // the staging groups follow the slots
+  if (make_map(&l->tm_w1, w1, groups * l->ffn1, l->H, 128)) return 1;
+  if (make_map(&l->tm_w2, w2, groups * l->H, l->I, 128)) return 1;
   for (auto& gph : l->graphs) cudaGraphExecDestroy(gph.exec);     // the tensor maps are baked into captured launches
   l->graphs.clear();
   l->have_weights = true;
@@ -560,7 +559,8 @@ static MetaArgs layer_meta_args(zepp_layer* l) {
   m.n_tiles = l->n_tiles; m.tile_group = l->tile_group; m.tile_row0 = l->tile_row0; m.tile_rows = l->tile_rows;
   m.tile_ready = l->tile_ready; m.max_tiles = l->max_tiles; m.recv_cap = l->cap; m.m_this = l->m_this;
   m.row_tok = l->row_tok; m.row_dst = l->row_dst; m.row_scale = l->row_scale; m.hidden = l->H;
-  m.group_order = nullptr;
+  m.group_order = l->cfg.swap ? l->sched : nullptr;
+  m.group_redirect = l->cfg.swap ? l->redirect : nullptr;
   m.staged = l->stage != nullptr ? 1 : 0;
   m.routing_flags = l->W > 1 ? l->routing_flags : nullptr;
   m.epoch_ptr = l->step_ctr; m.limit_ns = l->rt->wait_ns; m.status = l->status;
@@ -625,16 +625,6 @@ static int pass2_prepare(size_t bytes) {
   return 0;
 }
 
-static SwapMoveArgs layer_swap_args(zepp_layer* l) {
-  SwapMoveArgs a{};
-  a.block = l->swap_block; a.R = l->W; a.rank = l->rt->rank; a.cap = 8; a.world = l->W;
-  a.w1_vec = (size_t)l->ffn1 * l->H / 8; a.w2_vec = (size_t)l->H * l->I / 8;
-  a.w1 = (uint4*)l->w1_slots; a.w2 = (uint4*)l->w2_slots; a.w1_peers = l->w1_peers; a.w2_peers = l->w2_peers;
-  a.stag1 = (uint4*)l->stag1; a.stag2 = (uint4*)l->stag2; a.flags = l->swap_flag_dst; a.my_flags = l->swap_flags;
-  a.epoch_ptr = l->step_ctr; a.limit_ns = l->rt->wait_ns; a.counter = l->counters + 12; a.status = l->status;
-  return a;
-}
-
 // Does this step need the gathered loads?  Only the water-fill (some expert has more than one
 // replica) and the swap decision consume them.
 static bool needs_loads(const zepp_layer* l) { return l->c_max > 1 || l->cfg.swap != 0; }
@@ -678,27 +668,19 @@ extern "C" int zepp_layer_prepare_phase(zepp_layer* l, int phase, const int32_t*
   if (phase == 1) {
     if (!l->cfg.swap) return 0;
     // swap: one launch waits for the gathered loads, decides (rewrites p2l / l2p on the device), rebuilds the
-    // router's slot table and marks this rank's incoming slots; then the pull of the incoming experts into
-    // staging.  Nothing is read on the host.
+    // router's slot table and marks this rank's incoming slots.  The weights move under the GEMMs.  Nothing is
+    // read on the host.
     SwapArgs sa = swap_args(l->loads_all[0], l->p2l, l->l2p, l->lcnts, R, l->G, l->L, l->nlp,
                             (double)l->cfg.c_num / (double)l->cfg.c_den, 8, 32, l->swap_block);
     sa.loads_odd = l->loads_all[1]; sa.epoch_ptr = l->step_ctr; sa.loads_flags = R > 1 ? l->loads_flags : nullptr;
     sa.limit_ns = l->rt->wait_ns; sa.status = l->status; sa.slot_of = l->slot_of; sa.rank = me;
-    sa.sched = l->sched; sa.redirect = l->redirect;
+    sa.sched = l->sched; sa.redirect = l->redirect; sa.ready = l->w_ready;
     swap_decide_kernel<<<1, kSwapThreads, swap_smem(R, l->G, l->L, l->nlp), st>>>(sa);
-    LAUNCH_OK();
-    SwapMoveArgs sm = layer_swap_args(l);
-    swap_pull_kernel<<<l->rt->sm_count * 2, 256, 0, st>>>(sm);
     LAUNCH_OK();
     return 0;
   }
   if (phase == 2) {
     if (ids) { l->ids_in = ids; l->wts_in = wts; }
-    if (l->cfg.swap) {
-      SwapMoveArgs sm = layer_swap_args(l);
-      swap_commit_kernel<<<l->rt->sm_count * 2, 256, 0, st>>>(sm);
-      LAUNCH_OK();
-    }
     if (local_route(l)) return 0;        // done by the first metadata kernel
     if (l->c_max <= 1 && l->front_route) return 0;      // the front kernel's route blocks do it
     if (l->c_max <= 1) {
@@ -798,6 +780,13 @@ static GemmArgs layer_gemm_args(zepp_layer* l, bool first) {
     g.x_ptrs = l->stage_ptrs; g.x_ptrs_odd = l->stage_ptrs; g.x_self = nullptr; g.x_flags = l->push_flags;
   }
   g.recv = l->recv; g.tile_ready = l->tile_ready; g.tokens_per_rank = l->S; g.gather = 0;
+  if (l->cfg.swap) {
+    g.swap_block = l->swap_block; g.swap_ranks = l->W; g.swap_cap = kSwapCap; g.n_groups = l->gpe;
+    g.w_peers = first ? l->w1_peers : l->w2_peers;
+    g.w_slots = (uint4*)(first ? l->w1_slots : l->w2_slots);
+    g.w_vec = (unsigned long long)(first ? (size_t)l->ffn1 * l->H : (size_t)l->H * l->I) / 8;
+    g.w_ready = l->w_ready + (first ? 0 : kSwapCap);
+  }
   g.status = l->status; g.mbar_limit_ns = 2 * l->rt->wait_ns + 1000000000ull; g.flag_limit_ns = l->rt->wait_ns;
   return g;
 }
@@ -805,11 +794,13 @@ static GemmArgs layer_gemm_args(zepp_layer* l, bool first) {
 template <int MODE, bool LINES = false>
 static int launch_gemm(zepp_layer* l, const CUtensorMap& tw, const CUtensorMap* tx, GemmArgs& g, cudaStream_t st) {
   // more gather warps when most rows cross NVLink (latency-bound pulls), fewer when they are local
-  const int threads = g.gather ? 192 + 32 * (l->W >= 4 ? kMaxGatherWarps : 4) : 192;
+  const bool movers = g.swap_block != nullptr && l->W > 1;
+  if (!movers) g.swap_block = nullptr;
+  const int threads = g.gather ? 192 + 32 * (l->W >= 4 ? kMaxGatherWarps : 4) : (movers ? 192 + 32 * 4 : 192);
   const int grid = l->rt->sm_count;
   const size_t smem = GemmCfg<MODE>::kSmemBytes;
-  if (g.gather) {
-    // gather warps of one CTA feed the producers of others: every CTA must be resident
+  if (g.gather || movers) {
+    // gather / mover warps of one CTA feed the producers of others: every CTA must be resident
     void* args[] = {(void*)&tw, (void*)&tx[0], (void*)&tx[1], (void*)&tx[2], (void*)&g};
     CU_OK(cudaLaunchCooperativeKernel((const void*)moe_gemm_kernel<MODE, LINES>, dim3(grid), dim3(threads), args, smem, st));
     l->launches++;
@@ -818,6 +809,15 @@ static int launch_gemm(zepp_layer* l, const CUtensorMap& tw, const CUtensorMap* 
   moe_gemm_kernel<MODE, LINES><<<grid, threads, smem, st>>>(tw, tx[0], tx[1], tx[2], g);
   LAUNCH_OK();
   return 0;
+}
+
+static SwapCommitArgs layer_commit_args(zepp_layer* l) {
+  SwapCommitArgs c{};
+  if (!l->cfg.swap || l->W == 1) return c;
+  c.block = l->swap_block; c.R = l->W; c.rank = l->rt->rank; c.cap = kSwapCap; c.gpe = l->gpe;
+  c.w1_vec = (size_t)l->ffn1 * l->H / 8; c.w2_vec = (size_t)l->H * l->I / 8;
+  c.w1 = (uint4*)l->w1_slots; c.w2 = (uint4*)l->w2_slots;
+  return c;
 }
 
 static MoveArgs layer_move_args(zepp_layer* l) {
@@ -896,7 +896,7 @@ extern "C" int zepp_layer_forward_phase(zepp_layer* l, int phase, const void* x,
   if (phase == 3) {
     combine_reduce_kernel<<<l->rt->sm_count * 2, 256, 0, st>>>(l->panel, (__nv_bfloat16*)y, l->S, l->K, l->H,
                                                             l->W > 1 ? l->done_flags : nullptr, l->W, l->step_ctr,
-                                                            l->rt->wait_ns, l->status);
+                                                            l->rt->wait_ns, l->status, layer_commit_args(l));
     LAUNCH_OK();
     return 0;
   }

@@ -31,6 +31,7 @@ struct SwapArgs {
   int rank;
   int* sched;           // [gpe] out: schedule word per local group (bit 30 = slot received an expert this step)
   int* redirect;        // [gpe] out: group whose weights the GEMMs read: the group itself, or gpe + i for the i-th incoming expert
+  unsigned int* ready;  // [2 * cap] out: zeroed chunk counters of the staging entries (W1, then W2)
 };
 
 __device__ __forceinline__ bool band_out(const long long* Lr, int n, int L, double C) {
@@ -63,6 +64,9 @@ __device__ void swap_step_tables(const SwapArgs& a, const int* cur, int cnt, con
       a.slot_of[e] = p0;
     }
   }
+  if (threadIdx.x == 0 && a.epoch_ptr != nullptr) trace_mark(a.status, TR_DECIDE_END);
+  if (a.ready != nullptr)
+    for (int i = threadIdx.x; i < 2 * a.cap; i += blockDim.x) a.ready[i] = 0u;
   if (a.sched != nullptr) {
     for (int g = threadIdx.x; g < gpe; g += blockDim.x) {
       int hit = -1;
@@ -93,7 +97,9 @@ __global__ void __launch_bounds__(kSwapThreads) swap_decide_kernel(SwapArgs a) {
   if (a.epoch_ptr != nullptr) {
     const unsigned long long epoch = step_epoch(a.epoch_ptr, false);
     if (epoch & 1) a.loads = a.loads_odd;
+    if (tid == 0) trace_mark(a.status, TR_DECIDE);
     if (!block_wait_all(a.loads_flags, R, epoch, a.limit_ns, a.status, WAIT_LOADS)) return;
+    if (tid == 0) trace_mark(a.status, TR_DECIDE_GO);
   }
 
   for (int e = tid; e < G; e += nt) {
@@ -340,90 +346,37 @@ __global__ void lane_arm_kernel(const long long* out, int R, int rank, int nlp, 
 
 // ---------------------------------------------------------------------------------------
 // Weight movement of a decided swap (replaces the copies of python/zepp/swap.py:508-559 and
-// src/planner/lane_device.cu:82-163).  Two stream-ordered kernels on every rank, both driven by
-// the decision's result block on the device (no host read; a step without moves copies nothing):
-//   swap_pull_kernel    every rank pulls its incoming experts' W1 and W2 from the source ranks'
-//                       weight slots (peer loads over NVLink) into local staging, then tells every
-//                       rank that it no longer reads their old slots;
-//   swap_commit_kernel  waits for all ranks' "pulled" words, then copies staging into the destination
-//                       slots.  The step's GEMMs run after it, on the new placement.
-// An exchange overwrites a slot that a peer still has to read, hence the two phases.
+// src/planner/lane_device.cu:82-163).  Nothing runs ahead of the step for it: the two GEMM kernels pull the
+// incoming experts' W1 / W2 from the source ranks' slots into local staging groups with their spare warps while
+// the other groups compute (csrc/gemm.cuh), the step's moved-in groups are scheduled last and read from staging,
+// and the step's last kernel -- which starts its work only after every rank's combine GEMM has finished, so no
+// rank still reads a slot -- copies staging into the destination slots (swap_commit below).  All of it is driven by
+// the decision's result block on the device; a step without moves copies nothing.
 // ---------------------------------------------------------------------------------------
-struct SwapMoveArgs {
-  const long long* block;                    // swap decision result block
-  int R, rank, cap, world;
-  size_t w1_vec, w2_vec;                     // 16-byte vectors per slot of W1 / W2
-  uint4* w1;                                 // local slots [gpe][w1_vec] (group 0 = pad)
+struct SwapCommitArgs {
+  const long long* block;                    // swap decision result block (nullptr: no swap in this layer)
+  int R, rank, cap, gpe;
+  size_t w1_vec, w2_vec;                     // 16-byte vectors per group of W1 / W2
+  uint4* w1;                                 // [gpe + cap][w1_vec]: slot groups (group 0 = pad), then staging entries
   uint4* w2;
-  const uint4* const* w1_peers;              // [W] peers' slot bases
-  const uint4* const* w2_peers;
-  uint4* stag1;                              // [cap][w1_vec]
-  uint4* stag2;
-  PeerTable flags;                           // rank p's pulled words [W]
-  const unsigned long long* my_flags;        // this rank's pulled words
-  const unsigned long long* epoch_ptr;
-  unsigned long long limit_ns;
-  unsigned int* counter;
-  unsigned long long* status;
 };
 
-__device__ __forceinline__ int swap_my_moves(const SwapMoveArgs& a, const long long** mv) {
+// staging -> destination slots, by every thread of the calling grid
+__device__ __forceinline__ void swap_commit(const SwapCommitArgs& a) {
+  if (a.block == nullptr) return;
   const long long rounds = a.block[0];
   int cnt = rounds > 0 ? (int)a.block[3 + a.rank] : 0;
   if (cnt > a.cap) cnt = a.cap;
-  *mv = a.block + 3 + a.R + (size_t)a.rank * a.cap * 4;
-  return cnt;
-}
-
-__global__ void __launch_bounds__(256) swap_pull_kernel(SwapMoveArgs a) {
-  const unsigned long long epoch = a.epoch_ptr != nullptr ? *a.epoch_ptr : 0ull;
-  const long long* mv;
-  const int cnt = swap_my_moves(a, &mv);
-  const size_t per = a.w1_vec + a.w2_vec;
-  const size_t total = (size_t)cnt * per;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-    const int m = (int)(i / per);
-    const size_t o = i - (size_t)m * per;
-    const int src_rank = (int)mv[4 * m + 1], src_slot = (int)mv[4 * m + 2];
-    if (src_rank < 0 || src_rank >= a.world) continue;
-    if (o < a.w1_vec) a.stag1[(size_t)m * a.w1_vec + o] = a.w1_peers[src_rank][(size_t)(1 + src_slot) * a.w1_vec + o];
-    else a.stag2[(size_t)m * a.w2_vec + (o - a.w1_vec)] = a.w2_peers[src_rank][(size_t)(1 + src_slot) * a.w2_vec + (o - a.w1_vec)];
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence_system();
-    const unsigned int prev = atomicInc(a.counter, gridDim.x - 1);
-    if (prev == gridDim.x - 1) {
-      __threadfence_system();
-      for (int p = 0; p < a.world; ++p)
-        st_relaxed_sys(reinterpret_cast<unsigned long long*>(a.flags.ptr[p]) + a.rank, epoch);
-    }
-  }
-}
-
-__global__ void __launch_bounds__(256) swap_commit_kernel(SwapMoveArgs a) {
-  const unsigned long long epoch = a.epoch_ptr != nullptr ? *a.epoch_ptr : 0ull;
-  __shared__ int ok_s;
-  if (threadIdx.x == 0) ok_s = 1;
-  __syncthreads();
-  if (threadIdx.x < a.world && a.world > 1) {
-    if (!wait_epoch_geq(a.my_flags + threadIdx.x, epoch, a.limit_ns)) {
-      record_timeout(a.status, WAIT_BARRIER, threadIdx.x, (long long)epoch);
-      ok_s = 0;
-    }
-  }
-  __syncthreads();
-  if (!ok_s) return;
-  const long long* mv;
-  const int cnt = swap_my_moves(a, &mv);
+  if (cnt <= 0) return;
+  const long long* mv = a.block + 3 + a.R + (size_t)a.rank * a.cap * 4;
   const size_t per = a.w1_vec + a.w2_vec;
   const size_t total = (size_t)cnt * per;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const int m = (int)(i / per);
     const size_t o = i - (size_t)m * per;
     const int dst = (int)mv[4 * m];
-    if (o < a.w1_vec) a.w1[(size_t)(1 + dst) * a.w1_vec + o] = a.stag1[(size_t)m * a.w1_vec + o];
-    else a.w2[(size_t)(1 + dst) * a.w2_vec + (o - a.w1_vec)] = a.stag2[(size_t)m * a.w2_vec + (o - a.w1_vec)];
+    if (o < a.w1_vec) a.w1[(size_t)(1 + dst) * a.w1_vec + o] = a.w1[(size_t)(a.gpe + m) * a.w1_vec + o];
+    else a.w2[(size_t)(1 + dst) * a.w2_vec + (o - a.w1_vec)] = a.w2[(size_t)(a.gpe + m) * a.w2_vec + (o - a.w1_vec)];
   }
 }
 

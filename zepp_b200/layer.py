@@ -271,7 +271,8 @@ class EPMoE(torch.nn.Module):
 
     TRACE_NAMES = ("route", "pass1", "pass1_go", "pass2", "gemm1", "gemm1_x", "gemm1_end", "gemm2", "gemm2_end",
                    "reduce", "reduce_go", "reduce_end", "scan", "scan_counts", "scan_bases", "scan_demands",
-                   "scan_sched", "scan_end", None, None, None, None, "gather_end", "first_items")   # None: profile-build counters
+                   "scan_sched", "scan_end", "loads", "decide", "decide_go", "decide_end", "gather_end", "first_items")
+    # loads .. decide_end: the swap kernels that run before the routing (cycle counters in a profile build)
 
     def trace(self):
         """Device timeline of the last step: microseconds of each stamp after the step's first kernel."""
@@ -309,6 +310,44 @@ class EPMoE(torch.nn.Module):
         p2l = self._h.table("p2l").cpu()
         return Placement(p2l, rebuild_l2p(p2l, self.cfg.shape.num_experts, self.cfg.ranks), self.placement.lcnts,
                          dict(self.placement.stats))
+
+    def resize_capacities(self, demands=None, caps=None):
+        """Collective: rebuild this rank's buffers for larger capacities (`caps`, or the growth rule applied to the
+        `demands` of a step that raised CapacityExceeded -- they are identical on every rank), keeping the
+        placement the device tables hold now and the weights.  The reference grows collectively and plans the step
+        again (python/zepp/capacity.py:75-82, python/zepp/serving.py:434-451); callers repeat the step likewise."""
+        assert self._own_rt, "layers that share a caller's runtime cannot be resized"
+        from .capacity import grow
+        torch.cuda.synchronize()
+        if caps is None:
+            caps = grow(self.caps, demands, direct=self.cfg.comm_strategy == "direct")
+        cfg, shape = self.cfg, self.cfg.shape
+        placement = self.current_placement()
+        old_h, old_rt, w1, w2 = self._h, self._rt, self.w1, self.w2
+        self._barrier()
+        self.caps = caps
+        self._ccfg = make_cfg(cfg, caps, self.c_num, self.c_den)
+        self._rt = Runtime(self.rank, cfg.ranks, self.device.index, LayerHandle.arena_bytes(self._ccfg))
+        if cfg.ranks > 1:
+            self._rt.exchange_handles(self.group)
+        self._h = LayerHandle(self._rt, self._ccfg)
+        self._h.set_placement(placement)
+        self.placement = placement
+        if w1 is not None:
+            if cfg.swap:       # the weights live in the old arena's slots: copy them into the new ones
+                n1, n2 = self._h.weight_slots(cfg.groups_per_rank, shape.ffn1, shape.hidden, shape.ffn_hidden)
+                n1.copy_(w1)
+                n2.copy_(w2)
+                w1, w2 = n1, n2
+            self.set_weights(w1, w2)
+        old_h.destroy()
+        old_rt.destroy()
+        self._plan_views = None
+        tokens, self._tokens = self._tokens, cfg.max_tokens_per_rank
+        self.set_tokens(tokens)
+        self.redos += 1
+        self._barrier()
+        return caps
 
     def prep(self):
         """Per-iteration hygiene hook of the reference's benchmark loop: nothing to clear here (every
