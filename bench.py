@@ -550,6 +550,7 @@ def main():
         "median_step_period_us": case["median_step_period_us"],
         "host_enqueue_us_per_step": case["host_enqueue_us_per_step"],
         "steady_timeline_us_slowest_rank": steady,
+        "steady_timeline_us_all_ranks": case.get("steady_timeline_us_all_ranks"),
         "breakdown_us": br,
         "roofline_layer": case["roofline_layer"],
         "parity": case["parity"],

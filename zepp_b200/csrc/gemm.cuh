@@ -133,6 +133,258 @@ __device__ __forceinline__ __nv_bfloat16 gelu_bf16(float acc) {
   return __float2bfloat16_rn(0.5f * h * (1.0f + erff(h * 0.70710678118654752f)));
 }
 
+// Epilogue of one accumulator quadrant: thread <-> token row (TMEM lane), `t0` = TMEM address of the quadrant's
+// first column of the item, `out` = where this token's 128 / 256 output features start (nullptr: padding row).
+template <int MODE, bool LINES>
+__device__ __forceinline__ void gemm_epilogue_rows(const GemmArgs& a, uint32_t t0, __nv_bfloat16* out, float scale, int j,
+                                                   int lane, uint4* stg) {
+  constexpr int kFeatPerItemE = (MODE == MODE_DOWN_COMBINE) ? 2 * kTileM : kTileM;
+  if (MODE == MODE_GATE_UP_SWIGLU) {
+    for (int c0 = 0; c0 < kTileM; c0 += 32) {
+      uint32_t g[32], u[32];
+      tmem_ld_32x32(t0 + c0, g);
+      tmem_ld_32x32(t0 + kTileM + c0, u);
+      tmem_ld_wait();
+      if (out != nullptr) {
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          uint32_t w[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int n = q * 16 + e * 2;
+            const __nv_bfloat162 p = __halves2bfloat162(
+                swiglu_bf16(__uint_as_float(g[n]), __uint_as_float(u[n])),
+                swiglu_bf16(__uint_as_float(g[n + 1]), __uint_as_float(u[n + 1])));
+            w[e] = *reinterpret_cast<const uint32_t*>(&p);
+          }
+          st_global_v8(out + c0 + q * 16, w);
+        }
+      }
+    }
+  } else if (MODE == MODE_SINGLE_GELU) {
+    for (int c0 = 0; c0 < kTileM; c0 += 32) {
+      uint32_t g[32];
+      tmem_ld_32x32(t0 + c0, g);
+      tmem_ld_wait();
+      if (out != nullptr) {
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          uint32_t w[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int n = q * 16 + e * 2;
+            const __nv_bfloat162 p = __halves2bfloat162(gelu_bf16(__uint_as_float(g[n])),
+                                                        gelu_bf16(__uint_as_float(g[n + 1])));
+            w[e] = *reinterpret_cast<const uint32_t*>(&p);
+          }
+          st_global_v8(out + c0 + q * 16, w);
+        }
+      }
+    }
+  } else {
+    // reference rounding points (combine_kernels.cu:191-197): bf16 GEMM output, fp32 product with
+    // the top-k weight, bf16 row on the wire.  64 features = 128 contiguous bytes per step.
+    // An odd number of 128-feature blocks: the last item's second block lies past the expert's rows.
+    const int feat_end = min(kFeatPerItemE, a.w_rows_per_group - j * kFeatPerItemE);
+    for (int c0 = 0; c0 < feat_end; c0 += 64) {
+      uint32_t g[32], h[32];
+      tmem_ld_32x32(t0 + c0, g);
+      tmem_ld_32x32(t0 + c0 + 32, h);
+      tmem_ld_wait();
+      if (LINES) {
+        
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {           // this row's 64 features as eight 16-byte units
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int n = (q & 3) * 8 + e * 2;
+            const float v0 = __uint_as_float(q < 4 ? g[n] : h[n]);
+            const float v1 = __uint_as_float(q < 4 ? g[n + 1] : h[n + 1]);
+            const __nv_bfloat162 p = __floats2bfloat162_rn(bf16_round(v0) * scale, bf16_round(v1) * scale);
+            w[e] = *reinterpret_cast<const uint32_t*>(&p);
+          }
+          stg[lane * 8 + (q ^ (lane & 7))] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {           // four rows per instruction, eight lanes per row
+          const int r = 4 * i + (lane >> 3);
+          const int q = lane & 7;
+          const uint4 v = stg[r * 8 + (q ^ (r & 7))];
+          __nv_bfloat16* po = reinterpret_cast<__nv_bfloat16*>(
+              __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(out), r));
+          if (po != nullptr) *reinterpret_cast<uint4*>(po + c0 + q * 8) = v;
+        }
+        __syncwarp();                           // the next 64 features reuse the staging
+      } else if (out != nullptr) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint32_t w[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int n = (q & 1) * 16 + e * 2;
+            const float v0 = __uint_as_float(q < 2 ? g[n] : h[n]);
+            const float v1 = __uint_as_float(q < 2 ? g[n + 1] : h[n + 1]);
+            const __nv_bfloat162 p = __floats2bfloat162_rn(bf16_round(v0) * scale, bf16_round(v1) * scale);
+            w[e] = *reinterpret_cast<const uint32_t*>(&p);
+          }
+          st_global_v8(out + c0 + q * 16, w);
+        }
+      }
+    }
+  }
+}
+
+// Warps 6.. of a GEMM CTA: the fused dispatch gather (dispatch GEMM, overlap strategy), then the pull of a swap's
+// incoming experts.  `abort_flag` is the CTA-wide flag the other roles poll.
+template <int MODE>
+__device__ __forceinline__ void gemm_spare_warps(const GemmArgs& a, const int* s_pref, const int* s_row0, int n_tiles,
+                                                 int warp, int lane, unsigned long long epoch, int* abort_flag_p) {
+  volatile int* abortp = abort_flag_p;
+  // ------------------------------------------------------------------ gather warps (fused dispatch)
+  if (MODE != MODE_DOWN_COMBINE && a.gather) {
+    const int gw = warp - 6;                  // 0..gather warps-1
+    // every source must have published its x for this step
+    bool ok = true;
+    if (a.x_flags != nullptr && lane < a.world) {
+      if (!wait_epoch_geq(a.x_flags + lane, epoch, a.flag_limit_ns)) {
+        record_timeout(a.status, WAIT_X, lane, (long long)epoch);
+        ok = false;
+      }
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (blockIdx.x == 0 && gw == 0 && lane == 0) trace_mark(a.status, TR_GEMM1_X);
+    if (!ok) {
+      if (lane == 0) *abort_flag_p = 1;
+    } else {
+      // Rows are pulled in schedule order: row q of the step belongs to gather warp (q mod all
+      // gather warps), so every SM keeps loads in flight.  A warp first lists up to 32 of its rows
+      // (lane j keeps the j-th), fetches their source tokens in one round trip, then streams the
+      // rows two at a time.
+      const int vec_per_row = a.k_extent / 8;                 // 16-byte vectors per row
+      const int gather_warps = (int)(blockDim.x >> 5) - 6;
+      const int n_warps = gridDim.x * gather_warps;
+      const int my_warp = blockIdx.x * gather_warps + gw;
+      const int total_rows = s_pref[n_tiles];
+      for (int g0 = my_warp; g0 < total_rows; g0 += 32 * n_warps) {
+        {
+          {
+            // lane j takes this warp's j-th row of the list: a binary search of the prefix table
+            const int g = g0 + lane * n_warps;
+            int my_r = -1, my_ti = 0;
+            if (g < total_rows) {
+              int lo = 0, hi = n_tiles - 1;
+              while (lo < hi) {
+                const int mid = (lo + hi + 1) >> 1;
+                if (s_pref[mid] <= g) lo = mid; else hi = mid - 1;
+              }
+              my_ti = lo;
+              my_r = s_row0[lo] + (g - s_pref[lo]);
+            }
+            const int cnt = __popc(__ballot_sync(0xffffffffu, g < total_rows));
+            const int n = cnt;
+            const int tok = lane < n ? a.row_tok[my_r] : -1;
+            // two rows at a time (16 x 512 bytes of loads in flight per warp); a fence and the tile
+            // credits after every pair, so early tiles are complete early
+            for (int j0 = 0; j0 < n; j0 += 2) {
+              const int j1 = j0 + 2 < n ? j0 + 2 : n;
+              for (int j = j0; j < j1; j += 2) {
+                const uint4* srcA = nullptr;
+                const uint4* srcB = nullptr;
+                uint4* dstA = nullptr;
+                uint4* dstB = nullptr;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                  const int rr = __shfl_sync(0xffffffffu, my_r, (j + h) & 31);
+                  const int tk = __shfl_sync(0xffffffffu, tok, (j + h) & 31);
+                  if (j + h < j1) {
+                    const int src = tk >= 0 ? tk / a.tokens_per_rank : -1;
+                    if (src >= 0 && src < a.world) {
+                      const int t = tk - src * a.tokens_per_rank;
+                      const __nv_bfloat16* xb = (src == a.rank && a.x_self != nullptr)
+                                                    ? a.x_self : ((epoch & 1) ? a.x_ptrs_odd[src] : a.x_ptrs[src]);
+                      const uint4* sp = reinterpret_cast<const uint4*>(xb + (size_t)t * a.k_extent);
+                      uint4* dp = reinterpret_cast<uint4*>(a.recv + (size_t)rr * a.k_extent);
+                      if (h == 0) { srcA = sp; dstA = dp; } else { srcB = sp; dstB = dp; }
+                    } else if (lane == 0 && a.status != nullptr) {
+                      atomicOr(a.status + ST_ERROR, (unsigned long long)ERR_BAD_INDEX);
+                    }
+                  }
+                }
+                for (int v0 = 0; v0 < vec_per_row; v0 += 256) {
+                  uint4 ba[8], bb[8];
+#pragma unroll
+                  for (int q = 0; q < 8; ++q) {
+                    const int v = v0 + q * 32 + lane;
+                    if (v < vec_per_row) {
+                      if (srcA != nullptr) ba[q] = srcA[v];
+                      if (srcB != nullptr) bb[q] = srcB[v];
+                    }
+                  }
+#pragma unroll
+                  for (int q = 0; q < 8; ++q) {
+                    const int v = v0 + q * 32 + lane;
+                    if (v < vec_per_row) {
+                      if (dstA != nullptr) dstA[v] = ba[q];
+                      if (dstB != nullptr) dstB[v] = bb[q];
+                    }
+                  }
+                }
+              }
+              __threadfence();
+              __syncwarp();
+              if (lane >= j0 && lane < j1) atomicAdd(a.tile_ready + my_ti, 1u);
+            }
+          }
+        }
+      }
+      if (lane == 0) trace_mark_max(a.status, TR_GATHER_END);
+    }
+  }
+  if (a.swap_block != nullptr && !*abortp) {
+    // ---------------------------------------------------------------- movers (incoming experts of a swap)
+    const long long rounds = a.swap_block[0];
+    int cnt = rounds > 0 ? (int)a.swap_block[3 + a.rank] : 0;
+    if (cnt > a.swap_cap) cnt = a.swap_cap;
+    if (cnt > 0) {
+      const long long* mv = a.swap_block + 3 + a.swap_ranks + (size_t)a.rank * a.swap_cap * 4;
+      const int spare = (int)(blockDim.x >> 5) - 6;
+      const unsigned long long n_warps = (unsigned long long)gridDim.x * spare;
+      const unsigned long long me = (unsigned long long)blockIdx.x * spare + (warp - 6);
+      const unsigned long long per = (a.w_vec + kSwapChunkVecs - 1) / kSwapChunkVecs;
+      for (unsigned long long c = me; c < per * cnt; c += n_warps) {
+        const int m = (int)(c / per);
+        const unsigned long long v_lo = (c - (unsigned long long)m * per) * kSwapChunkVecs;
+        const unsigned long long v_hi = v_lo + kSwapChunkVecs < a.w_vec ? v_lo + kSwapChunkVecs : a.w_vec;
+        const int src_rank = (int)mv[4 * m + 1], src_slot = (int)mv[4 * m + 2];
+        if (src_rank >= 0 && src_rank < a.world) {
+          const uint4* sp = a.w_peers[src_rank] + (unsigned long long)(1 + src_slot) * a.w_vec;
+          uint4* dp = a.w_slots + (unsigned long long)(a.n_groups + m) * a.w_vec;
+          for (unsigned long long v0 = v_lo; v0 < v_hi; v0 += 256) {
+            uint4 buf[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const unsigned long long v = v0 + q * 32 + lane;
+              if (v < v_hi) buf[q] = sp[v];
+            }
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const unsigned long long v = v0 + q * 32 + lane;
+              if (v < v_hi) dp[v] = buf[q];
+            }
+          }
+        } else if (lane == 0 && a.status != nullptr) {
+          atomicOr(a.status + ST_ERROR, (unsigned long long)ERR_BAD_INDEX);
+        }
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) atomicAdd(a.w_ready + m, 1u);
+      }
+    }
+  }
+}
+
 // LINES (combine GEMM only): the epilogue writes whole 128-byte lines of the destination rows instead
 // of 32-byte pieces.  Each epilogue warp stages its 32 token rows x 64 features in its own 4 KB of
 // shared memory (16-byte units XOR-swizzled by the row, so neither the row-wise writes nor the
@@ -418,101 +670,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
       tc_fence_after();
       if (quad * 32 < rows) {                   // warps whose 32 token rows are all padding skip the reads
         const uint32_t t0 = tmem_base + acc * Cfg::kAccCols + ((uint32_t)(quad * 32) << 16);
-        if (MODE == MODE_GATE_UP_SWIGLU) {
-          for (int c0 = 0; c0 < kTileM; c0 += 32) {
-            uint32_t g[32], u[32];
-            tmem_ld_32x32(t0 + c0, g);
-            tmem_ld_32x32(t0 + kTileM + c0, u);
-            tmem_ld_wait();
-            if (out != nullptr) {
-#pragma unroll
-              for (int q = 0; q < 2; ++q) {
-                uint32_t w[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                  const int n = q * 16 + e * 2;
-                  const __nv_bfloat162 p = __halves2bfloat162(
-                      swiglu_bf16(__uint_as_float(g[n]), __uint_as_float(u[n])),
-                      swiglu_bf16(__uint_as_float(g[n + 1]), __uint_as_float(u[n + 1])));
-                  w[e] = *reinterpret_cast<const uint32_t*>(&p);
-                }
-                st_global_v8(out + c0 + q * 16, w);
-              }
-            }
-          }
-        } else if (MODE == MODE_SINGLE_GELU) {
-          for (int c0 = 0; c0 < kTileM; c0 += 32) {
-            uint32_t g[32];
-            tmem_ld_32x32(t0 + c0, g);
-            tmem_ld_wait();
-            if (out != nullptr) {
-#pragma unroll
-              for (int q = 0; q < 2; ++q) {
-                uint32_t w[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                  const int n = q * 16 + e * 2;
-                  const __nv_bfloat162 p = __halves2bfloat162(gelu_bf16(__uint_as_float(g[n])),
-                                                              gelu_bf16(__uint_as_float(g[n + 1])));
-                  w[e] = *reinterpret_cast<const uint32_t*>(&p);
-                }
-                st_global_v8(out + c0 + q * 16, w);
-              }
-            }
-          }
-        } else {
-          // reference rounding points (combine_kernels.cu:191-197): bf16 GEMM output, fp32 product with
-          // the top-k weight, bf16 row on the wire.  64 features = 128 contiguous bytes per step.
-          // An odd number of 128-feature blocks: the last item's second block lies past the expert's rows.
-          const int feat_end = min(Cfg::kFeatPerItem, a.w_rows_per_group - j * Cfg::kFeatPerItem);
-          for (int c0 = 0; c0 < feat_end; c0 += 64) {
-            uint32_t g[32], h[32];
-            tmem_ld_32x32(t0 + c0, g);
-            tmem_ld_32x32(t0 + c0 + 32, h);
-            tmem_ld_wait();
-            if (LINES) {
-              uint4* stg = s_lines[warp - 2];
-#pragma unroll
-              for (int q = 0; q < 8; ++q) {           // this row's 64 features as eight 16-byte units
-                uint32_t w[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  const int n = (q & 3) * 8 + e * 2;
-                  const float v0 = __uint_as_float(q < 4 ? g[n] : h[n]);
-                  const float v1 = __uint_as_float(q < 4 ? g[n + 1] : h[n + 1]);
-                  const __nv_bfloat162 p = __floats2bfloat162_rn(bf16_round(v0) * scale, bf16_round(v1) * scale);
-                  w[e] = *reinterpret_cast<const uint32_t*>(&p);
-                }
-                stg[lane * 8 + (q ^ (lane & 7))] = make_uint4(w[0], w[1], w[2], w[3]);
-              }
-              __syncwarp();
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {           // four rows per instruction, eight lanes per row
-                const int r = 4 * i + (lane >> 3);
-                const int q = lane & 7;
-                const uint4 v = stg[r * 8 + (q ^ (r & 7))];
-                __nv_bfloat16* po = reinterpret_cast<__nv_bfloat16*>(
-                    __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(out), r));
-                if (po != nullptr) *reinterpret_cast<uint4*>(po + c0 + q * 8) = v;
-              }
-              __syncwarp();                           // the next 64 features reuse the staging
-            } else if (out != nullptr) {
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                uint32_t w[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                  const int n = (q & 1) * 16 + e * 2;
-                  const float v0 = __uint_as_float(q < 2 ? g[n] : h[n]);
-                  const float v1 = __uint_as_float(q < 2 ? g[n + 1] : h[n + 1]);
-                  const __nv_bfloat162 p = __floats2bfloat162_rn(bf16_round(v0) * scale, bf16_round(v1) * scale);
-                  w[e] = *reinterpret_cast<const uint32_t*>(&p);
-                }
-                st_global_v8(out + c0 + q * 16, w);
-              }
-            }
-          }
-        }
+        gemm_epilogue_rows<MODE, LINES>(a, t0, out, scale, j, lane, LINES ? s_lines[warp - 2] : nullptr);
       }
       tc_fence_before();
       __syncwarp();
@@ -523,147 +681,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     ZEPP_PROF(if (blockIdx.x == 0 && warp == 2 && lane == 0 && a.status != nullptr && MODE != MODE_DOWN_COMBINE) {
       a.status[TR_PROF_EPI_BUSY] = (unsigned long long)prof_busy; a.status[TR_PROF_EPI_WAIT] = (unsigned long long)prof_wait; })
   } else {
-    // ------------------------------------------------------------------ gather warps (fused dispatch)
-    if (MODE != MODE_DOWN_COMBINE && a.gather) {
-      const int gw = warp - 6;                  // 0..gather warps-1
-      // every source must have published its x for this step
-      bool ok = true;
-      if (a.x_flags != nullptr && lane < a.world) {
-        if (!wait_epoch_geq(a.x_flags + lane, epoch, a.flag_limit_ns)) {
-          record_timeout(a.status, WAIT_X, lane, (long long)epoch);
-          ok = false;
-        }
-      }
-      ok = __all_sync(0xffffffffu, ok);
-      if (blockIdx.x == 0 && gw == 0 && lane == 0) trace_mark(a.status, TR_GEMM1_X);
-      if (!ok) {
-        if (lane == 0) abort_flag = 1;
-      } else {
-        // Rows are pulled in schedule order: row q of the step belongs to gather warp (q mod all
-        // gather warps), so every SM keeps loads in flight.  A warp first lists up to 32 of its rows
-        // (lane j keeps the j-th), fetches their source tokens in one round trip, then streams the
-        // rows two at a time.
-        const int vec_per_row = a.k_extent / 8;                 // 16-byte vectors per row
-        const int gather_warps = (int)(blockDim.x >> 5) - 6;
-        const int n_warps = gridDim.x * gather_warps;
-        const int my_warp = blockIdx.x * gather_warps + gw;
-        const int total_rows = s_pref[n_tiles];
-        for (int g0 = my_warp; g0 < total_rows; g0 += 32 * n_warps) {
-          {
-            {
-              // lane j takes this warp's j-th row of the list: a binary search of the prefix table
-              const int g = g0 + lane * n_warps;
-              int my_r = -1, my_ti = 0;
-              if (g < total_rows) {
-                int lo = 0, hi = n_tiles - 1;
-                while (lo < hi) {
-                  const int mid = (lo + hi + 1) >> 1;
-                  if (s_pref[mid] <= g) lo = mid; else hi = mid - 1;
-                }
-                my_ti = lo;
-                my_r = s_row0[lo] + (g - s_pref[lo]);
-              }
-              const int cnt = __popc(__ballot_sync(0xffffffffu, g < total_rows));
-              const int n = cnt;
-              const int tok = lane < n ? a.row_tok[my_r] : -1;
-              // two rows at a time (16 x 512 bytes of loads in flight per warp); a fence and the tile
-              // credits after every pair, so early tiles are complete early
-              for (int j0 = 0; j0 < n; j0 += 2) {
-                const int j1 = j0 + 2 < n ? j0 + 2 : n;
-                for (int j = j0; j < j1; j += 2) {
-                  const uint4* srcA = nullptr;
-                  const uint4* srcB = nullptr;
-                  uint4* dstA = nullptr;
-                  uint4* dstB = nullptr;
-#pragma unroll
-                  for (int h = 0; h < 2; ++h) {
-                    const int rr = __shfl_sync(0xffffffffu, my_r, (j + h) & 31);
-                    const int tk = __shfl_sync(0xffffffffu, tok, (j + h) & 31);
-                    if (j + h < j1) {
-                      const int src = tk >= 0 ? tk / a.tokens_per_rank : -1;
-                      if (src >= 0 && src < a.world) {
-                        const int t = tk - src * a.tokens_per_rank;
-                        const __nv_bfloat16* xb = (src == a.rank && a.x_self != nullptr)
-                                                      ? a.x_self : ((epoch & 1) ? a.x_ptrs_odd[src] : a.x_ptrs[src]);
-                        const uint4* sp = reinterpret_cast<const uint4*>(xb + (size_t)t * a.k_extent);
-                        uint4* dp = reinterpret_cast<uint4*>(a.recv + (size_t)rr * a.k_extent);
-                        if (h == 0) { srcA = sp; dstA = dp; } else { srcB = sp; dstB = dp; }
-                      } else if (lane == 0 && a.status != nullptr) {
-                        atomicOr(a.status + ST_ERROR, (unsigned long long)ERR_BAD_INDEX);
-                      }
-                    }
-                  }
-                  for (int v0 = 0; v0 < vec_per_row; v0 += 256) {
-                    uint4 ba[8], bb[8];
-#pragma unroll
-                    for (int q = 0; q < 8; ++q) {
-                      const int v = v0 + q * 32 + lane;
-                      if (v < vec_per_row) {
-                        if (srcA != nullptr) ba[q] = srcA[v];
-                        if (srcB != nullptr) bb[q] = srcB[v];
-                      }
-                    }
-#pragma unroll
-                    for (int q = 0; q < 8; ++q) {
-                      const int v = v0 + q * 32 + lane;
-                      if (v < vec_per_row) {
-                        if (dstA != nullptr) dstA[v] = ba[q];
-                        if (dstB != nullptr) dstB[v] = bb[q];
-                      }
-                    }
-                  }
-                }
-                __threadfence();
-                __syncwarp();
-                if (lane >= j0 && lane < j1) atomicAdd(a.tile_ready + my_ti, 1u);
-              }
-            }
-          }
-        }
-        if (lane == 0) trace_mark_max(a.status, TR_GATHER_END);
-      }
-    }
-    if (a.swap_block != nullptr && !*abortp) {
-      // ---------------------------------------------------------------- movers (incoming experts of a swap)
-      const long long rounds = a.swap_block[0];
-      int cnt = rounds > 0 ? (int)a.swap_block[3 + a.rank] : 0;
-      if (cnt > a.swap_cap) cnt = a.swap_cap;
-      if (cnt > 0) {
-        const long long* mv = a.swap_block + 3 + a.swap_ranks + (size_t)a.rank * a.swap_cap * 4;
-        const int spare = (int)(blockDim.x >> 5) - 6;
-        const unsigned long long n_warps = (unsigned long long)gridDim.x * spare;
-        const unsigned long long me = (unsigned long long)blockIdx.x * spare + (warp - 6);
-        const unsigned long long per = (a.w_vec + kSwapChunkVecs - 1) / kSwapChunkVecs;
-        for (unsigned long long c = me; c < per * cnt; c += n_warps) {
-          const int m = (int)(c / per);
-          const unsigned long long v_lo = (c - (unsigned long long)m * per) * kSwapChunkVecs;
-          const unsigned long long v_hi = v_lo + kSwapChunkVecs < a.w_vec ? v_lo + kSwapChunkVecs : a.w_vec;
-          const int src_rank = (int)mv[4 * m + 1], src_slot = (int)mv[4 * m + 2];
-          if (src_rank >= 0 && src_rank < a.world) {
-            const uint4* sp = a.w_peers[src_rank] + (unsigned long long)(1 + src_slot) * a.w_vec;
-            uint4* dp = a.w_slots + (unsigned long long)(a.n_groups + m) * a.w_vec;
-            for (unsigned long long v0 = v_lo; v0 < v_hi; v0 += 256) {
-              uint4 buf[8];
-#pragma unroll
-              for (int q = 0; q < 8; ++q) {
-                const unsigned long long v = v0 + q * 32 + lane;
-                if (v < v_hi) buf[q] = sp[v];
-              }
-#pragma unroll
-              for (int q = 0; q < 8; ++q) {
-                const unsigned long long v = v0 + q * 32 + lane;
-                if (v < v_hi) dp[v] = buf[q];
-              }
-            }
-          } else if (lane == 0 && a.status != nullptr) {
-            atomicOr(a.status + ST_ERROR, (unsigned long long)ERR_BAD_INDEX);
-          }
-          __threadfence();
-          __syncwarp();
-          if (lane == 0) atomicAdd(a.w_ready + m, 1u);
-        }
-      }
-    }
+    gemm_spare_warps<MODE>(a, s_pref, s_row0, n_tiles, warp, lane, epoch, &abort_flag);
   }
 
   // ------------------------------------------------------------------ teardown

@@ -79,6 +79,7 @@ struct MetaArgs {
   int hidden;               // H (row_dst is an element offset into the home's [S*K, H] panel)
   int staged;               // 1: row_tok holds (source, staging slot) instead of (source, token)
   const int* group_order;   // [gpe] schedule word per group (bit 30 = moved-in slot: its tiles go last) or nullptr
+  int tile_rows_max;        // token rows of a GEMM tile: 128 (one CTA per tile) or 256 (CTA pairs); 0 = 128
   const int* group_redirect;// [gpe] group whose weights a group's tiles read (a staging entry for a moved-in slot) or nullptr
   // exchange wait
   const unsigned long long* routing_flags;
@@ -375,7 +376,8 @@ __device__ void meta_scan_body(MetaArgs& a, int* sm, bool bases_in_place) {
       me = s_splits[g0 + e];
       late = a.group_order != nullptr ? ((a.group_order[e] >> 30) & 1) : 0;
     }
-    const int nt = (me + kTileRowsMax - 1) / kTileRowsMax;
+    const int tile_rows = a.tile_rows_max > 0 ? a.tile_rows_max : kTileRowsMax;
+    const int nt = (me + tile_rows - 1) / tile_rows;
     int tot_early, tot_late;
     const int pre_early = block_exclusive_scan(late ? 0 : nt, warp_tot, &tot_early);
     const int pre_late = block_exclusive_scan(late ? nt : 0, warp_tot, &tot_late);
@@ -385,8 +387,8 @@ __device__ void meta_scan_body(MetaArgs& a, int* sm, bool bases_in_place) {
       const int slot = first + t;
       if (slot < a.max_tiles) {
         a.tile_group[slot] = a.group_redirect != nullptr ? a.group_redirect[e] : e;
-        a.tile_row0[slot] = off + t * kTileRowsMax;
-        a.tile_rows[slot] = min(kTileRowsMax, me - t * kTileRowsMax);
+        a.tile_row0[slot] = off + t * tile_rows;
+        a.tile_rows[slot] = min(tile_rows, me - t * tile_rows);
         a.tile_ready[slot] = 0u;
       }
     }

@@ -16,6 +16,7 @@
 #include "common.cuh"
 #include "front.cuh"
 #include "gemm.cuh"
+#include "gemm_pair.cuh"
 #include "layer_kernels.cuh"
 #include "meta.cuh"
 #include "planner.cuh"
@@ -55,6 +56,8 @@ static size_t pass2_smem(int tokens_per_tile, int K, int E_virt);
 static int pass2_prepare(size_t bytes);
 static int meta_fused_prepare(zepp_layer* l);
 static int front_push_blocks(const zepp_layer* l, int n_route);
+static int pair_kernels_prepare(zepp_layer* l);
+static void choose_gemm_kind(zepp_layer* l);
 
 extern "C" const char* zepp_last_error(void) { return g_err.c_str(); }
 extern "C" int zepp_abi_version(void) { return 1; }
@@ -209,6 +212,9 @@ struct zepp_layer {
   zepp_layer_cfg cfg{};
   int G, K, H, I, ffn1, W, L, NN, S, SK, nlp, gpe, E_virt, cap, max_tiles, tokens_per_tile, tiles_per_src;
   int S_max;                                  // tokens per rank the buffers were sized for (S: the current bucket)
+  bool use_pairs = false;                     // the GEMMs run on CTA pairs (256-row token tiles)
+  int pairs_mode = -1;                        // ZEPP_B200_PAIRS: 1 / 0 force the pair kernels on / off, -1 = by row count
+  int pair_grid = 0;                          // CTAs of a pair-kernel launch (2 x resident clusters)
   bool meta_fused = false;                    // the metadata runs as one cooperative launch (grid fits the device)
   unsigned long long epoch = 0;
   int64_t launches = 0;
@@ -456,6 +462,15 @@ extern "C" int zepp_layer_create(zepp_rt* rt, const zepp_layer_cfg* c, zepp_laye
   if (meta_fused_prepare(l)) { delete l; return 1; }
   if (l->cfg.swap && swap_decide_prepare()) { delete l; return 1; }
   {
+    // CTA-pair GEMMs: attributes, resident cluster count, and whether this layer's row counts want them
+    const char* pm = getenv("ZEPP_B200_PAIRS");
+    if (pm != nullptr && (pm[0] == '0' || pm[0] == '1')) l->pairs_mode = pm[0] - '0';
+    if (l->cfg.act == 1 && pair_kernels_prepare(l)) { delete l; return 1; }
+    choose_gemm_kind(l);
+    if (getenv("ZEPP_B200_VERBOSE") != nullptr)
+      fprintf(stderr, "[zepp_b200] layer rank %d/%d: GEMMs on %s (pair grid %d), metadata %s, front blocks %d\n", rt->rank,
+              l->W, l->use_pairs ? "CTA pairs" : "single CTAs", l->pair_grid, l->meta_fused ? "fused" : "two launches",
+              l->front_blocks_max);
     const char* g = getenv("ZEPP_B200_GRAPHS");     // "0": launch the step's kernels one by one instead of as a graph
     if (g != nullptr && g[0] == '0') l->use_graphs = false;
     // The combine GEMM's epilogue stages rows in shared memory and stores whole 128-byte lines when its rows go
@@ -503,6 +518,7 @@ extern "C" int zepp_layer_set_tokens(zepp_layer* l, int tokens) {
   l->S = tokens;
   l->SK = tokens * l->K;
   l->tiles_per_src = (tokens + l->tokens_per_tile - 1) / l->tokens_per_tile;
+  choose_gemm_kind(l);
   return meta_fused_prepare(l);
 }
 
@@ -559,6 +575,7 @@ static MetaArgs layer_meta_args(zepp_layer* l) {
   m.n_tiles = l->n_tiles; m.tile_group = l->tile_group; m.tile_row0 = l->tile_row0; m.tile_rows = l->tile_rows;
   m.tile_ready = l->tile_ready; m.max_tiles = l->max_tiles; m.recv_cap = l->cap; m.m_this = l->m_this;
   m.row_tok = l->row_tok; m.row_dst = l->row_dst; m.row_scale = l->row_scale; m.hidden = l->H;
+  m.tile_rows_max = l->use_pairs ? kPairTileRows : kTileRowsMax;
   m.group_order = l->cfg.swap ? l->sched : nullptr;
   m.group_redirect = l->cfg.swap ? l->redirect : nullptr;
   m.staged = l->stage != nullptr ? 1 : 0;
@@ -581,6 +598,20 @@ static size_t meta_smem(int R, int NN, int E_virt) {
 static size_t fused_smem(const zepp_layer* l) {
   return meta_fused_smem_ints(l->W, l->NN, l->E_virt, l->tokens_per_tile, l->K) * sizeof(int);
 }
+// CTA pairs pay once an expert's rows fill more than one 128-row tile: with fewer rows the second CTA of a pair
+// would only halve the weight bytes each SM stages, which the HBM-bound small-batch case does not need.
+static void choose_gemm_kind(zepp_layer* l) {
+  const long long rows_per_expert = (long long)l->S * l->K * l->W / (l->G > 0 ? l->G : 1);
+  bool pairs = l->cfg.act == 1 && l->pair_grid >= 2 && rows_per_expert >= 160;
+  if (l->pairs_mode == 0) pairs = false;
+  if (l->pairs_mode == 1) pairs = l->cfg.act == 1 && l->pair_grid >= 2;
+  if (pairs != l->use_pairs) {
+    for (auto& gph : l->graphs) cudaGraphExecDestroy(gph.exec);
+    l->graphs.clear();
+  }
+  l->use_pairs = pairs;
+}
+
 // Push blocks a front launch can add beside its metadata and route blocks (0: the push stays a kernel of its own).
 static int front_push_blocks(const zepp_layer* l, int n_route) {
   int n = l->front_blocks_max - (l->W * l->tiles_per_src + 1) - n_route;
@@ -797,17 +828,46 @@ static int launch_gemm(zepp_layer* l, const CUtensorMap& tw, const CUtensorMap* 
   const bool movers = g.swap_block != nullptr && l->W > 1;
   if (!movers) g.swap_block = nullptr;
   const int threads = g.gather ? 192 + 32 * (l->W >= 4 ? kMaxGatherWarps : 4) : (movers ? 192 + 32 * 4 : 192);
-  const int grid = l->rt->sm_count;
-  const size_t smem = GemmCfg<MODE>::kSmemBytes;
-  if (g.gather || movers) {
-    // gather / mover warps of one CTA feed the producers of others: every CTA must be resident
-    void* args[] = {(void*)&tw, (void*)&tx[0], (void*)&tx[1], (void*)&tx[2], (void*)&g};
-    CU_OK(cudaLaunchCooperativeKernel((const void*)moe_gemm_kernel<MODE, LINES>, dim3(grid), dim3(threads), args, smem, st));
-    l->launches++;
-    return 0;
+  const bool coop = g.gather || movers;     // spare warps of one CTA feed the producers of others: every CTA must be resident
+  void* args[] = {(void*)&tw, (void*)&tx[0], (void*)&tx[1], (void*)&tx[2], (void*)&g};
+  cudaLaunchConfig_t cfg{};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;
+  attr[0].val.cooperative = 1;
+  cfg.blockDim = dim3(threads);
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = coop ? 1 : 0;
+  if constexpr (MODE != MODE_SINGLE_GELU) {
+    if (l->use_pairs) {
+      cfg.gridDim = dim3(l->pair_grid);
+      cfg.dynamicSmemBytes = kPairSmemBytes;
+      CU_OK(cudaLaunchKernelExC(&cfg, (const void*)moe_gemm_pair_kernel<MODE, LINES>, args));
+      l->launches++;
+      return 0;
+    }
   }
-  moe_gemm_kernel<MODE, LINES><<<grid, threads, smem, st>>>(tw, tx[0], tx[1], tx[2], g);
-  LAUNCH_OK();
+  cfg.gridDim = dim3(l->rt->sm_count);
+  cfg.dynamicSmemBytes = GemmCfg<MODE>::kSmemBytes;
+  CU_OK(cudaLaunchKernelExC(&cfg, (const void*)moe_gemm_kernel<MODE, LINES>, args));
+  l->launches++;
+  return 0;
+}
+
+// Attributes of the CTA-pair kernels and how many pairs the device keeps resident (one CTA per SM).
+static int pair_kernels_prepare(zepp_layer* l) {
+  CU_OK(cudaFuncSetAttribute(moe_gemm_pair_kernel<MODE_GATE_UP_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes));
+  CU_OK(cudaFuncSetAttribute(moe_gemm_pair_kernel<MODE_DOWN_COMBINE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes));
+  CU_OK(cudaFuncSetAttribute(moe_gemm_pair_kernel<MODE_DOWN_COMBINE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes));
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(l->rt->sm_count & ~1);
+  cfg.blockDim = dim3(192 + 32 * kMaxGatherWarps);
+  cfg.dynamicSmemBytes = kPairSmemBytes;
+  int clusters = 0;
+  cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, (const void*)moe_gemm_pair_kernel<MODE_DOWN_COMBINE, true>, &cfg);
+  if (e != cudaSuccess) { cudaGetLastError(); clusters = 0; }
+  if (clusters > l->rt->sm_count / 2) clusters = l->rt->sm_count / 2;
+  l->pair_grid = 2 * clusters;
   return 0;
 }
 
