@@ -148,23 +148,6 @@ __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async;" ::: "memory");
 }
 
-// Bulk asynchronous copies shared -> global (plain, non-multicast; the destination may be a peer GPU's memory):
-// the copy engine streams the bytes out while the issuing warp goes on.  Sizes and both addresses are multiples
-// of 16 bytes.  A thread's own shared-memory writes need fence_proxy_async_smem() before its copy reads them.
-__device__ __forceinline__ void fence_proxy_async_smem() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-__device__ __forceinline__ void bulk_store_s2g(void* gmem_dst, const void* smem_src, uint32_t bytes) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst), "r"(smem_u32(smem_src)),
-               "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-// all of this thread's committed copies have READ their shared-memory source (it may be overwritten)
-__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-// all of this thread's committed copies are complete
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-
 // one 32-byte store (a whole sector): sm_100 has 256-bit global stores; the address is 32-byte aligned
 __device__ __forceinline__ void st_global_v8(void* p, const uint32_t (&w)[8]) {
   asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]),

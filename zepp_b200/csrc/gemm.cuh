@@ -36,8 +36,6 @@ constexpr int kXTileBytes = kTileN * kTileK * 2;   // 16 KB
 constexpr int kAccStages = 2;
 constexpr int kMaxGatherWarps = 8;     // warps 6.. of a dispatch GEMM CTA in fused mode (4 or 8, chosen at launch)
 constexpr int kMaxTilesSmem = 1024;   // token tiles of one rank and step held in shared memory
-constexpr int kStageRowUnits = 33;    // 16-byte units between staged epilogue rows: 512 bytes + 16 (no bank conflicts)
-constexpr int kStageWarpBytes = 32 * kStageRowUnits * 16;        // one epilogue warp's 32 rows
 constexpr int kSwapChunkVecs = 2048;  // 16-byte vectors a mover warp copies per credit (32 KB)
 
 // -DZEPP_GEMM_PROFILE: CTA 0 of the dispatch GEMM sums, in SM cycles, how long its MMA thread waited for
@@ -115,8 +113,6 @@ struct GemmCfg {
   static constexpr int kStageBytes = (kDual ? 2 : 1) * kWTileBytes + kXTileBytes;
   static constexpr int kStages = kDual ? 4 : 6;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024;   // + alignment slack
-  // the staged combine epilogue: one stage fewer, plus the four epilogue warps' staging rows
-  static constexpr int kSmemBytesLines = (kStages - 1) * kStageBytes + 4 * kStageWarpBytes + 1024;
   static constexpr int kAccCols = kDual ? 2 * kTileN : kTileN;      // TMEM columns per accumulator stage
   static constexpr int kTmemCols = kAccStages * kAccCols;           // 512 or 256
 };
@@ -190,15 +186,15 @@ __device__ __forceinline__ void gemm_epilogue_rows(const GemmArgs& a, uint32_t t
     // the top-k weight, bf16 row on the wire.  64 features = 128 contiguous bytes per step.
     // An odd number of 128-feature blocks: the last item's second block lies past the expert's rows.
     const int feat_end = min(kFeatPerItemE, a.w_rows_per_group - j * kFeatPerItemE);
-    if (LINES) bulk_wait_read_all();          // the previous item's copy has read this thread's staging row
     for (int c0 = 0; c0 < feat_end; c0 += 64) {
       uint32_t g[32], h[32];
       tmem_ld_32x32(t0 + c0, g);
       tmem_ld_32x32(t0 + c0 + 32, h);
       tmem_ld_wait();
       if (LINES) {
+        
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {           // this row's 64 features as eight 16-byte units of its staging row
+        for (int q = 0; q < 8; ++q) {           // this row's 64 features as eight 16-byte units
           uint32_t w[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -208,8 +204,19 @@ __device__ __forceinline__ void gemm_epilogue_rows(const GemmArgs& a, uint32_t t
             const __nv_bfloat162 p = __floats2bfloat162_rn(bf16_round(v0) * scale, bf16_round(v1) * scale);
             w[e] = *reinterpret_cast<const uint32_t*>(&p);
           }
-          stg[lane * kStageRowUnits + (c0 >> 3) + q] = make_uint4(w[0], w[1], w[2], w[3]);
+          stg[lane * 8 + (q ^ (lane & 7))] = make_uint4(w[0], w[1], w[2], w[3]);
         }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {           // four rows per instruction, eight lanes per row
+          const int r = 4 * i + (lane >> 3);
+          const int q = lane & 7;
+          const uint4 v = stg[r * 8 + (q ^ (r & 7))];
+          __nv_bfloat16* po = reinterpret_cast<__nv_bfloat16*>(
+              __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(out), r));
+          if (po != nullptr) *reinterpret_cast<uint4*>(po + c0 + q * 8) = v;
+        }
+        __syncwarp();                           // the next 64 features reuse the staging
       } else if (out != nullptr) {
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -225,12 +232,6 @@ __device__ __forceinline__ void gemm_epilogue_rows(const GemmArgs& a, uint32_t t
           st_global_v8(out + c0 + q * 16, w);
         }
       }
-    }
-    if (LINES) {
-      // the whole row slice (up to 512 contiguous bytes) leaves as one asynchronous bulk copy
-      fence_proxy_async_smem();
-      if (out != nullptr) bulk_store_s2g(out, stg + lane * kStageRowUnits, (uint32_t)feat_end * 2u);
-      bulk_commit_group();
     }
   }
 }
@@ -384,18 +385,19 @@ __device__ __forceinline__ void gemm_spare_warps(const GemmArgs& a, const int* s
   }
 }
 
-// LINES (combine GEMM only): the epilogue stages every token's row slice of the item (256 features = 512
-// contiguous bytes) in shared memory and sends it as ONE asynchronous bulk copy per row instead of 32-byte
-// register stores.  Meant for destination panels on peer GPUs: NVLink carries few large writes far better than
-// many small ones, and the warps convert the next accumulator while the copy engine streams the rows out.  The
-// staging (4 warps x 32 rows x 528 bytes) takes the place of one operand stage: three stages instead of four.
+// LINES (combine GEMM only): the epilogue writes whole 128-byte lines of the destination rows instead
+// of 32-byte pieces.  Each epilogue warp stages its 32 token rows x 64 features in its own 4 KB of
+// shared memory (16-byte units XOR-swizzled by the row, so neither the row-wise writes nor the
+// line-wise reads conflict) and eight lanes then store one row's 128 contiguous bytes.  Meant for
+// destination panels on peer GPUs, where NVLink carries a few large writes far better than many
+// 32-byte ones.
 template <int MODE, bool LINES = false>
 __global__ void __launch_bounds__(192 + 32 * kMaxGatherWarps, 1)
 moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x32,
                 const __grid_constant__ CUtensorMap tm_x64, const __grid_constant__ CUtensorMap tm_x128,
                 const GemmArgs a) {
   using Cfg = GemmCfg<MODE>;
-  constexpr int STAGES = LINES ? Cfg::kStages - 1 : Cfg::kStages;
+  constexpr int STAGES = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
 
@@ -408,7 +410,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
   __shared__ int s_row0[kMaxTilesSmem], s_gr[kMaxTilesSmem];      // first row; (group << 9) | rows
   __shared__ int s_pref[kMaxTilesSmem + 1];                        // rows before tile i in schedule order
   static_assert(!LINES || MODE == MODE_DOWN_COMBINE, "line staging belongs to the combine epilogue");
-  uint4* s_lines = reinterpret_cast<uint4*>(smem + STAGES * Cfg::kStageBytes);   // LINES: staging behind the operand stages
+  __shared__ uint4 s_lines[LINES ? 4 : 1][LINES ? 256 : 1];        // per epilogue warp: 32 rows x 8 units of 16 bytes
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -668,17 +670,13 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
       tc_fence_after();
       if (quad * 32 < rows) {                   // warps whose 32 token rows are all padding skip the reads
         const uint32_t t0 = tmem_base + acc * Cfg::kAccCols + ((uint32_t)(quad * 32) << 16);
-        gemm_epilogue_rows<MODE, LINES>(a, t0, out, scale, j, lane, s_lines + (warp - 2) * (kStageWarpBytes / 16));
+        gemm_epilogue_rows<MODE, LINES>(a, t0, out, scale, j, lane, LINES ? s_lines[warp - 2] : nullptr);
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
       if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
       ZEPP_PROF(prof_busy += clock64() - prof_t; prof_t = clock64();)
-    }
-    if (LINES) {
-      bulk_wait_all();            // this thread's row copies are complete before the CTA reports the step's rows as sent
-      fence_proxy_async();
     }
     ZEPP_PROF(if (blockIdx.x == 0 && warp == 2 && lane == 0 && a.status != nullptr && MODE != MODE_DOWN_COMBINE) {
       a.status[TR_PROF_EPI_BUSY] = (unsigned long long)prof_busy; a.status[TR_PROF_EPI_WAIT] = (unsigned long long)prof_wait; })

@@ -24,8 +24,6 @@ constexpr int kPairTileRows = 2 * kTileN;     // token rows of a pair's tile
 constexpr int kPairStages = 6;
 constexpr int kPairStageBytes = kWTileBytes + kXTileBytes;          // 32 KB: this CTA's weight rows + its token rows
 constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + 1024;
-constexpr int kPairStagesLines = 4;           // the staged combine epilogue gives two operand stages to its staging rows
-constexpr int kPairSmemBytesLines = kPairStagesLines * kPairStageBytes + 4 * kStageWarpBytes + 1024;
 constexpr int kPairAccCols = 2 * kTileN;                            // 256 fp32 columns per accumulator stage
 constexpr int kPairTmemCols = kAccStages * kPairAccCols;            // 512
 
@@ -36,7 +34,7 @@ moe_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
                      const GemmArgs a) {
   static_assert(MODE == MODE_GATE_UP_SWIGLU || MODE == MODE_DOWN_COMBINE, "the pair kernel computes two weight blocks per item");
   static_assert(!LINES || MODE == MODE_DOWN_COMBINE, "line staging belongs to the combine epilogue");
-  constexpr int STAGES = LINES ? kPairStagesLines : kPairStages;
+  constexpr int STAGES = kPairStages;
   constexpr int kFeatPerItem = (MODE == MODE_DOWN_COMBINE) ? 2 * kTileM : kTileM;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -49,7 +47,7 @@ moe_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
   __shared__ int abort_flag;
   __shared__ int s_row0[kMaxTilesSmem], s_gr[kMaxTilesSmem];      // first row; (group << 9) | rows (1..256)
   __shared__ int s_pref[kMaxTilesSmem + 1];                        // rows before tile i in schedule order
-  uint4* s_lines = reinterpret_cast<uint4*>(smem + STAGES * kPairStageBytes);     // LINES: staging behind the operand stages
+  __shared__ uint4 s_lines[LINES ? 4 : 1][LINES ? 256 : 1];        // per epilogue warp: 32 rows x 8 units of 16 bytes
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -270,16 +268,12 @@ moe_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
       tc_fence_after();
       if ((int)cta * kTileN + quad * 32 < rows) {      // warps whose 32 token rows are all padding skip the reads
         const uint32_t t0 = tmem_base + acc * kPairAccCols + ((uint32_t)(quad * 32) << 16);
-        gemm_epilogue_rows<MODE, LINES>(a, t0, out, scale, j, lane, s_lines + (warp - 2) * (kStageWarpBytes / 16));
+        gemm_epilogue_rows<MODE, LINES>(a, t0, out, scale, j, lane, LINES ? s_lines[warp - 2] : nullptr);
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(lead_acc_empty + 8u * (uint32_t)acc);
       if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
-    }
-    if (LINES) {
-      bulk_wait_all();
-      fence_proxy_async();
     }
   } else {
     gemm_spare_warps<MODE>(a, s_pref, s_row0, n_tiles, warp, lane, epoch, &abort_flag);

@@ -261,7 +261,7 @@ struct zepp_layer {
   unsigned long long* step_ctr = nullptr;     // device-resident step counter (epoch of the running step)
   int c_max = 1;                              // largest replica count of the resident placement
   bool use_graphs = true;
-  bool combine_lines = false;                 // combine epilogue sends staged row slices as bulk copies
+  bool combine_lines = false;                 // combine epilogue writes staged 128-byte lines
   const void* fuse_x = nullptr;       // x of a whole-step call, published by the routing kernel
   const void* x_fused = nullptr;
   cudaStream_t capture_stream = nullptr;
@@ -457,7 +457,7 @@ extern "C" int zepp_layer_create(zepp_rt* rt, const zepp_layer_cfg* c, zepp_laye
   CU_OK(cudaFuncSetAttribute(moe_gemm_kernel<MODE_DOWN_COMBINE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              GemmCfg<MODE_DOWN_COMBINE>::kSmemBytes));
   CU_OK(cudaFuncSetAttribute(moe_gemm_kernel<MODE_DOWN_COMBINE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             GemmCfg<MODE_DOWN_COMBINE>::kSmemBytesLines));
+                             GemmCfg<MODE_DOWN_COMBINE>::kSmemBytes));
   if (pass2_prepare(pass2_smem(l->tokens_per_tile, l->K, l->E_virt))) { delete l; return 1; }
   if (meta_fused_prepare(l)) { delete l; return 1; }
   if (l->cfg.swap && swap_decide_prepare()) { delete l; return 1; }
@@ -473,8 +473,8 @@ extern "C" int zepp_layer_create(zepp_rt* rt, const zepp_layer_cfg* c, zepp_laye
               l->front_blocks_max);
     const char* g = getenv("ZEPP_B200_GRAPHS");     // "0": launch the step's kernels one by one instead of as a graph
     if (g != nullptr && g[0] == '0') l->use_graphs = false;
-    // The combine GEMM's epilogue stages rows in shared memory and sends each row slice as one bulk copy when its
-    // rows go to panels on other ranks; "1" / "0" force that form on / off.
+    // The combine GEMM's epilogue stages rows in shared memory and stores whole 128-byte lines when its rows go
+    // to panels on other ranks; "1" / "0" force that form on / off.
     const char* cs = getenv("ZEPP_B200_COMBINE_STAGED");
     l->combine_lines = l->W > 1;
     if (cs != nullptr && (cs[0] == '0' || cs[0] == '1')) l->combine_lines = cs[0] == '1';
@@ -841,14 +841,14 @@ static int launch_gemm(zepp_layer* l, const CUtensorMap& tw, const CUtensorMap* 
   if constexpr (MODE != MODE_SINGLE_GELU) {
     if (l->use_pairs) {
       cfg.gridDim = dim3(l->pair_grid);
-      cfg.dynamicSmemBytes = LINES ? kPairSmemBytesLines : kPairSmemBytes;
+      cfg.dynamicSmemBytes = kPairSmemBytes;
       CU_OK(cudaLaunchKernelExC(&cfg, (const void*)moe_gemm_pair_kernel<MODE, LINES>, args));
       l->launches++;
       return 0;
     }
   }
   cfg.gridDim = dim3(l->rt->sm_count);
-  cfg.dynamicSmemBytes = LINES ? GemmCfg<MODE>::kSmemBytesLines : GemmCfg<MODE>::kSmemBytes;
+  cfg.dynamicSmemBytes = GemmCfg<MODE>::kSmemBytes;
   CU_OK(cudaLaunchKernelExC(&cfg, (const void*)moe_gemm_kernel<MODE, LINES>, args));
   l->launches++;
   return 0;
@@ -858,11 +858,11 @@ static int launch_gemm(zepp_layer* l, const CUtensorMap& tw, const CUtensorMap* 
 static int pair_kernels_prepare(zepp_layer* l) {
   CU_OK(cudaFuncSetAttribute(moe_gemm_pair_kernel<MODE_GATE_UP_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes));
   CU_OK(cudaFuncSetAttribute(moe_gemm_pair_kernel<MODE_DOWN_COMBINE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes));
-  CU_OK(cudaFuncSetAttribute(moe_gemm_pair_kernel<MODE_DOWN_COMBINE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytesLines));
+  CU_OK(cudaFuncSetAttribute(moe_gemm_pair_kernel<MODE_DOWN_COMBINE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes));
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(l->rt->sm_count & ~1);
   cfg.blockDim = dim3(192 + 32 * kMaxGatherWarps);
-  cfg.dynamicSmemBytes = kPairSmemBytesLines > kPairSmemBytes ? kPairSmemBytesLines : kPairSmemBytes;
+  cfg.dynamicSmemBytes = kPairSmemBytes;
   int clusters = 0;
   cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, (const void*)moe_gemm_pair_kernel<MODE_DOWN_COMBINE, true>, &cfg);
   if (e != cudaSuccess) { cudaGetLastError(); clusters = 0; }
