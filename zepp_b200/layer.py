@@ -69,6 +69,22 @@ _ERR_NAMES = {1: "a device-side wait ran out", 2: "the step exceeded the buffer 
               4: "an index table entry was out of range", 8: "the router could not place all rows"}
 
 
+def plan_layer(cfg, sizing_routing, pool_routing, device, group):
+    """Set-up planning shared by every way of building a layer: the placement from the pool routing's demand, and
+    buffer capacities that hold the sizing batch on that placement and on every placement its swap orbit can reach
+    (python/zepp/layer.py:53-62).  Collective over `group` when it is a process group (capacities are max-reduced)."""
+    shape = cfg.shape
+    demand = demand_histogram(pool_routing.to(device), cfg.ranks_per_node, shape.num_experts).cpu()
+    placement = solve_placement(demand, cfg.ranks_per_node, cfg.slots_per_rank)
+    sizing = sizing_routing.cpu()
+    reachable = [placement]
+    if cfg.swap:
+        load = torch.bincount(sizing.reshape(-1).long(), minlength=shape.num_experts)
+        reachable.extend(swap_orbit(load, placement, cfg.ranks_per_node, cfg.slots_per_rank, cfg.router_c, device=device))
+    caps = compute_capacities(sizing, reachable, cfg.slots_per_rank, cfg.ranks_per_node, cfg.router_c, group, device=device)
+    return placement, caps
+
+
 class EPMoE(torch.nn.Module):
     def __init__(self, cfg: EPMoEConfig, group, sizing_routing, pool_routing, probs_own=None,
                  dtype=torch.bfloat16, _runtime=None):
@@ -83,14 +99,7 @@ class EPMoE(torch.nn.Module):
         R, L, nlp = cfg.ranks, cfg.ranks_per_node, cfg.slots_per_rank
         assert group.size() == R
         self.device = torch.device("cuda", torch.cuda.current_device())
-        hist = demand_histogram(pool_routing.to(self.device), L, shape.num_experts).cpu()
-        self.placement = solve_placement(hist, L, nlp)
-        sizing_cpu = sizing_routing.cpu()
-        placements = [self.placement]
-        if cfg.swap:
-            load_g = torch.bincount(sizing_cpu.reshape(-1).long(), minlength=shape.num_experts)
-            placements += swap_orbit(load_g, self.placement, L, nlp, cfg.router_c, device=self.device)
-        self.caps = compute_capacities(sizing_cpu, placements, nlp, L, cfg.router_c, group, device=self.device)
+        self.placement, self.caps = plan_layer(cfg, sizing_routing, pool_routing, self.device, group)
         self.redos = 0
         self.gpu_plan = True
         self.c_num, self.c_den = c_rational(cfg.router_c)
@@ -130,12 +139,11 @@ class EPMoE(torch.nn.Module):
         else:
             w1 = torch.zeros(gpe, shape.ffn1, shape.hidden, dtype=self.dtype, device=self.device)
             w2 = torch.zeros(gpe, shape.hidden, shape.ffn_hidden, dtype=self.dtype, device=self.device)
-        for i in range(nlp):
-            e = int(self.placement.p2l[self.rank * nlp + i])
-            if e < 0:
-                continue
-            w1[1 + i].copy_(w1_of(e).to(self.dtype))
-            w2[1 + i].copy_(w2_of(e).to(self.dtype))
+        mine = self.placement.p2l[self.rank * nlp:(self.rank + 1) * nlp].tolist()
+        for group_index, expert in enumerate(mine, start=1):          # group 0 is the pad group
+            if expert >= 0:
+                w1[group_index].copy_(w1_of(expert).to(self.dtype))
+                w2[group_index].copy_(w2_of(expert).to(self.dtype))
         self.set_weights(w1, w2)
 
     def set_weights(self, w1_slots, w2_slots):
@@ -366,14 +374,7 @@ def make_local_layers(cfg: EPMoEConfig, sizing_routing, pool_routing, wait_limit
     long as every rank finishes a phase before any rank starts the next: use `local_step`."""
     R = cfg.ranks
     dev = torch.device("cuda", torch.cuda.current_device())
-    hist = demand_histogram(pool_routing.to(dev), cfg.ranks_per_node, cfg.shape.num_experts).cpu()
-    pl = solve_placement(hist, cfg.ranks_per_node, cfg.slots_per_rank)
-    placements = [pl]
-    if cfg.swap:
-        load_g = torch.bincount(sizing_routing.reshape(-1).long(), minlength=cfg.shape.num_experts)
-        placements += swap_orbit(load_g, pl, cfg.ranks_per_node, cfg.slots_per_rank, cfg.router_c, device=dev)
-    caps = compute_capacities(sizing_routing.cpu(), placements, cfg.slots_per_rank, cfg.ranks_per_node, cfg.router_c,
-                              None, device=dev)
+    _, caps = plan_layer(cfg, sizing_routing, pool_routing, dev, None)
     nbytes = EPMoE.arena_bytes(cfg, caps)
     rts = [Runtime(r, R, dev.index, nbytes) for r in range(R)]
     if wait_limit_ms:

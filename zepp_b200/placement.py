@@ -40,34 +40,39 @@ def demand_histogram(topk_all: torch.Tensor, ranks_per_node: int, num_experts: i
 
 
 def _replica_counts(load, nodes, total_slots):
+    """Instances per expert: one each, then the spare slots go one at a time to the expert whose per-instance share
+    (load << SHARE_BITS) // instances is largest (ties: lower id), never more than one instance per node."""
     G = len(load)
-    assert total_slots >= G, "fewer slots than experts"
-    c = [1] * G
-    limit = min(nodes, total_slots)
-    heap = [(-(load[g] << SHARE_BITS), g) for g in range(G)]
-    heapq.heapify(heap)
-    spare = total_slots - G
-    while spare > 0 and heap:
-        _, g = heapq.heappop(heap)
-        if c[g] >= limit:
-            continue
-        c[g] += 1
-        spare -= 1
-        if c[g] < limit:
-            heapq.heappush(heap, (-((load[g] << SHARE_BITS) // c[g]), g))
-    return c
+    if total_slots < G:
+        raise AssertionError("fewer slots than experts")
+    most = min(nodes, total_slots)
+    counts = [1] * G
+    if most <= 1:
+        return counts
+    # max-heap on the current share; an entry is pushed again only while its expert may still grow
+    queue = [(-(int(v) << SHARE_BITS), g) for g, v in enumerate(load)]
+    heapq.heapify(queue)
+    for _ in range(total_slots - G):
+        if not queue:
+            break
+        _, g = heapq.heappop(queue)
+        counts[g] += 1
+        if counts[g] < most:
+            heapq.heappush(queue, (-((int(load[g]) << SHARE_BITS) // counts[g]), g))
+    return counts
 
 
 def rebuild_l2p(p2l: torch.Tensor, num_experts: int, ranks: int) -> torch.Tensor:
-    """l2p [G, R] from p2l: every expert's physical slots in ascending order."""
-    p = p2l.cpu().numpy().astype(np.int64)
-    l2p = np.full((num_experts, ranks), -1, dtype=np.int32)
-    slots = np.nonzero(p >= 0)[0]
-    order = np.argsort(p[slots], kind="stable")
-    e, s = p[slots][order], slots[order]
-    first = np.searchsorted(e, e, side="left")
-    l2p[e, np.arange(e.size) - first] = s
-    return torch.from_numpy(l2p)
+    """l2p [G, R] from p2l: every expert's physical slots in ascending order, -1 behind them."""
+    table = [[] for _ in range(num_experts)]
+    for slot, expert in enumerate(p2l.cpu().tolist()):       # ascending slots, so each list comes out sorted
+        if expert >= 0:
+            table[expert].append(slot)
+    l2p = torch.full((num_experts, ranks), -1, dtype=torch.int32)
+    for expert, slots in enumerate(table):
+        if slots:
+            l2p[expert, :len(slots)] = torch.tensor(slots, dtype=torch.int32)
+    return l2p
 
 
 def solve_placement(hist: torch.Tensor, ranks_per_node: int, slots_per_rank: int) -> Placement:

@@ -13,13 +13,16 @@ from ._ext import C
 
 
 def c_rational(Cf: float):
-    """Routing slack C as (num, den) with den a power of two; C must be a dyadic rational."""
-    assert math.isfinite(Cf) and Cf >= 0, f"router_c must be finite and >= 0: {Cf}"
-    den = 1 << 16
-    num = int(round(Cf * den))
-    assert abs(num / den - Cf) < 1e-12, f"router_c {Cf} is not a dyadic rational"
-    g = math.gcd(num, den) if num else den
-    return num // g, den // g
+    """Routing slack C as an exact fraction (num, den) in lowest terms with den a power of two (at most 2**16);
+    a C that is not such a dyadic rational is an assertion error, as in the reference (python/zepp/routing.py:26-33)."""
+    from fractions import Fraction
+    if not (math.isfinite(Cf) and Cf >= 0):
+        raise AssertionError(f"router_c must be finite and >= 0: {Cf}")
+    scaled = round(Cf * 65536)
+    if abs(scaled / 65536 - Cf) >= 1e-12:
+        raise AssertionError(f"router_c {Cf} is not a dyadic rational")
+    frac = Fraction(scaled, 65536)
+    return frac.numerator, frac.denominator
 
 
 @dataclass
