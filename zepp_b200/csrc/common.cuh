@@ -55,6 +55,13 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
 __device__ __forceinline__ void trace_mark(unsigned long long* status, int slot) {
   if (status != nullptr) status[slot] = globaltimer_ns();
 }
+// Stamps inside a kernel's serial sections (each costs the stamping thread a globaltimer read that the block then
+// waits for at its next barrier): compiled in only with -DZEPP_FINE_TRACE.
+#ifdef ZEPP_FINE_TRACE
+#define ZEPP_FINE_MARK(status, slot) trace_mark(status, slot)
+#else
+#define ZEPP_FINE_MARK(status, slot) ((void)0)
+#endif
 __device__ __forceinline__ void trace_mark_max(unsigned long long* status, int slot) {
   if (status != nullptr) atomicMax(status + slot, globaltimer_ns());
 }

@@ -238,13 +238,15 @@ __device__ __forceinline__ void gemm_epilogue_rows(const GemmArgs& a, uint32_t t
 
 // Warps 6.. of a GEMM CTA: the fused dispatch gather (dispatch GEMM, overlap strategy), then the pull of a swap's
 // incoming experts.  `abort_flag` is the CTA-wide flag the other roles poll.
+// `gw` of `gather_warps`: this warp's place among the CTA's gathering warps (the spare warps, and -- before their
+// first accumulator can possibly be ready -- the four epilogue warps).
 template <int MODE>
 __device__ __forceinline__ void gemm_spare_warps(const GemmArgs& a, const int* s_pref, const int* s_row0, int n_tiles,
-                                                 int warp, int lane, unsigned long long epoch, int* abort_flag_p) {
+                                                 int warp, int lane, unsigned long long epoch, int* abort_flag_p,
+                                                 int gw, int gather_warps, bool movers) {
   volatile int* abortp = abort_flag_p;
   // ------------------------------------------------------------------ gather warps (fused dispatch)
   if (MODE != MODE_DOWN_COMBINE && a.gather) {
-    const int gw = warp - 6;                  // 0..gather warps-1
     // every source must have published its x for this step
     bool ok = true;
     if (a.x_flags != nullptr && lane < a.world) {
@@ -263,7 +265,6 @@ __device__ __forceinline__ void gemm_spare_warps(const GemmArgs& a, const int* s
       // (lane j keeps the j-th), fetches their source tokens in one round trip, then streams the
       // rows two at a time.
       const int vec_per_row = a.k_extent / 8;                 // 16-byte vectors per row
-      const int gather_warps = (int)(blockDim.x >> 5) - 6;
       const int n_warps = gridDim.x * gather_warps;
       const int my_warp = blockIdx.x * gather_warps + gw;
       const int total_rows = s_pref[n_tiles];
@@ -342,7 +343,7 @@ __device__ __forceinline__ void gemm_spare_warps(const GemmArgs& a, const int* s
       if (lane == 0) trace_mark_max(a.status, TR_GATHER_END);
     }
   }
-  if (a.swap_block != nullptr && !*abortp) {
+  if (movers && a.swap_block != nullptr && !*abortp) {
     // ---------------------------------------------------------------- movers (incoming experts of a swap)
     const long long rounds = a.swap_block[0];
     int cnt = rounds > 0 ? (int)a.swap_block[3 + a.rank] : 0;
@@ -629,6 +630,11 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     // that token's output row.  Nothing is staged in shared memory and the warps never synchronise
     // with each other.
     const int quad = warp & 3;                  // TMEM lane quadrant this warp may read
+    if (MODE != MODE_DOWN_COMBINE && a.gather) {
+      // no accumulator can be ready before the step's rows are assembled: help assemble them first
+      const int spare = (int)(blockDim.x >> 5) - 6;
+      gemm_spare_warps<MODE>(a, s_pref, s_row0, n_tiles, warp, lane, epoch, &abort_flag, spare + (warp - 2), spare + 4, false);
+    }
     const int tok = quad * 32 + lane;           // token row inside the tile
     int acc = 0;
     uint32_t acc_phase = 0;
@@ -681,7 +687,8 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     ZEPP_PROF(if (blockIdx.x == 0 && warp == 2 && lane == 0 && a.status != nullptr && MODE != MODE_DOWN_COMBINE) {
       a.status[TR_PROF_EPI_BUSY] = (unsigned long long)prof_busy; a.status[TR_PROF_EPI_WAIT] = (unsigned long long)prof_wait; })
   } else {
-    gemm_spare_warps<MODE>(a, s_pref, s_row0, n_tiles, warp, lane, epoch, &abort_flag);
+    gemm_spare_warps<MODE>(a, s_pref, s_row0, n_tiles, warp, lane, epoch, &abort_flag, warp - 6,
+                           (int)(blockDim.x >> 5) - 6 + (MODE != MODE_DOWN_COMBINE ? 4 : 0), true);
   }
 
   // ------------------------------------------------------------------ teardown

@@ -229,6 +229,11 @@ moe_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
   } else if (warp < 6) {
     // ------------------------------------------------------------------ epilogue (4 warps per CTA, own TMEM)
     const int quad = warp & 3;
+    if (MODE != MODE_DOWN_COMBINE && a.gather) {
+      // no accumulator can be ready before the step's rows are assembled: help assemble them first
+      const int spare = (int)(blockDim.x >> 5) - 6;
+      gemm_spare_warps<MODE>(a, s_pref, s_row0, n_tiles, warp, lane, epoch, &abort_flag, spare + (warp - 2), spare + 4, false);
+    }
     const int tok = (int)cta * kTileN + quad * 32 + lane;           // token row inside the pair's tile
     int acc = 0;
     uint32_t acc_phase = 0;
@@ -276,7 +281,8 @@ moe_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
       if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
     }
   } else {
-    gemm_spare_warps<MODE>(a, s_pref, s_row0, n_tiles, warp, lane, epoch, &abort_flag);
+    gemm_spare_warps<MODE>(a, s_pref, s_row0, n_tiles, warp, lane, epoch, &abort_flag, warp - 6,
+                           (int)(blockDim.x >> 5) - 6 + (MODE != MODE_DOWN_COMBINE ? 4 : 0), true);
   }
 
   // ------------------------------------------------------------------ teardown

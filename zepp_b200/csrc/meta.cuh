@@ -302,30 +302,35 @@ __device__ void meta_scan_body(MetaArgs& a, int* sm, bool bases_in_place) {
   __syncthreads();
   if (threadIdx.x == 0) trace_mark(a.status, TR_SCAN);
   for (int i = threadIdx.x; i < R * R; i += blockDim.x) chunks[i] = 0;
+  for (int e = threadIdx.x; e < E_virt; e += blockDim.x) s_splits[e] = 0;
   __syncthreads();
-  // per source splits, totals, chunk table
-  for (int e = threadIdx.x; e < E_virt; e += blockDim.x) {
-    int tot = 0;
-    const int d = e / a.gpe;
-    for (int s = 0; s < R; ++s) {
-      int acc = 0;
-      for (int tb = 0; tb < a.tiles_per_src; ++tb) acc += __ldcg(a.tile_hist + (size_t)(s * a.tiles_per_src + tb) * E_virt + e);
-      a.sps[s * E_virt + e] = acc;
-      if (acc) atomicAdd(&chunks[s * R + d], acc);
-      tot += acc;
+  // per source splits, totals, chunk table: one (source, expert) pair per thread, its tiles' counts loaded
+  // independently of each other (the loop is unrolled so that the loads are in flight together)
+  for (int idx = threadIdx.x; idx < R * E_virt; idx += blockDim.x) {
+    const int s = idx / E_virt, e = idx - s * E_virt;
+    const int* col = a.tile_hist + (size_t)s * a.tiles_per_src * E_virt + e;
+    int acc = 0;
+#pragma unroll 8
+    for (int tb = 0; tb < a.tiles_per_src; ++tb) acc += __ldcg(col + (size_t)tb * E_virt);
+    a.sps[idx] = acc;
+    if (acc) {
+      atomicAdd(&chunks[s * R + e / a.gpe], acc);
+      atomicAdd(&s_splits[e], acc);
     }
-    a.splits[e] = tot;
-    s_splits[e] = tot;
   }
   for (int i = threadIdx.x; i < R * ucw; i += blockDim.x) {
     const int s = i / ucw, d = i - s * ucw;
+    const int* col = a.tile_uc + (size_t)s * a.tiles_per_src * ucw + d;
     int acc = 0;
-    for (int tb = 0; tb < a.tiles_per_src; ++tb) acc += __ldcg(a.tile_uc + (size_t)(s * a.tiles_per_src + tb) * ucw + d);
+#pragma unroll 8
+    for (int tb = 0; tb < a.tiles_per_src; ++tb) acc += __ldcg(col + (size_t)tb * ucw);
     a.uc[i] = acc;
     s_uc[i] = acc;
   }
   __syncthreads();
-  if (threadIdx.x == 0) trace_mark(a.status, TR_SCAN_COUNTS);
+  for (int e = threadIdx.x; e < E_virt; e += blockDim.x) a.splits[e] = s_splits[e];
+  __syncthreads();
+  if (threadIdx.x == 0) ZEPP_FINE_MARK(a.status, TR_SCAN_COUNTS);
   // exclusive scan of splits -> expert_base (E_virt <= 4 * blockDim)
   {
     const int per = (E_virt + blockDim.x - 1) / blockDim.x;
@@ -340,7 +345,7 @@ __device__ void meta_scan_body(MetaArgs& a, int* sm, bool bases_in_place) {
     if (threadIdx.x == 0) { a.expert_base[E_virt] = total; s_base[E_virt] = total; }
   }
   __syncthreads();
-  if (threadIdx.x == 0) trace_mark(a.status, TR_SCAN_BASES);
+  if (threadIdx.x == 0) ZEPP_FINE_MARK(a.status, TR_SCAN_BASES);
   if (bases_in_place)
   for (int e = threadIdx.x; e < E_virt; e += blockDim.x) {      // tile histograms -> tile bases, in place
     int run = s_base[e];
@@ -351,7 +356,7 @@ __device__ void meta_scan_body(MetaArgs& a, int* sm, bool bases_in_place) {
     }
   }
   if (threadIdx.x == 0) {
-    trace_mark(a.status, TR_SCAN_DEMANDS);
+    ZEPP_FINE_MARK(a.status, TR_SCAN_DEMANDS);
     long long out[8];
     demands_from_chunks(chunks, s_uc, R, a.L, a.relay_slots, a.direct, a.caps, out);
     for (int i = 0; i < 8; ++i) a.demands[i] = out[i];
@@ -362,7 +367,7 @@ __device__ void meta_scan_body(MetaArgs& a, int* sm, bool bases_in_place) {
     }
   }
   __syncthreads();
-  if (threadIdx.x == 0) trace_mark(a.status, TR_SCAN_SCHED);
+  if (threadIdx.x == 0) ZEPP_FINE_MARK(a.status, TR_SCAN_SCHED);
   // ---- this rank's GEMM schedule: token tiles of its groups in row order, one thread per group;
   //      groups marked as moved-in (bit 30 of their schedule word) go last (their weights land late)
   if (a.n_tiles != nullptr) {
