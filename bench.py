@@ -421,8 +421,26 @@ def run_e2e(ctx, case, steps, warmup):
     ctx.barrier()
     ms = ctx.max_over_ranks(t0.elapsed_time(t1)) / steps
     layer.check()
+    # the same host <-> device copies alone (no step between them): what the host links deliver when every rank of
+    # the box copies at once -- the floor of the end-to-end step time
+    ctx.barrier()
+    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    c0.record()
+    for i in range(steps):
+        b = i & 1
+        with torch.cuda.stream(s_in):
+            ids_in[b].copy_(ids_pin[i % n_batches], non_blocking=True)
+            w_in[b].copy_(w_pin[i % n_batches], non_blocking=True)
+            x_in[b].copy_(xs_host[i % n_x], non_blocking=True)
+        with torch.cuda.stream(s_out):
+            y_pins[b].copy_(y_dev[b], non_blocking=True)
+    main.wait_stream(s_in)
+    main.wait_stream(s_out)
+    c1.record()
+    ctx.barrier()
+    ms_copy = ctx.max_over_ranks(c0.elapsed_time(c1)) / steps
     h2d = int(ids_pin[0].numel() * 4 + w_pin[0].numel() * 4 + xs_host[0].numel() * 2)
-    return ms, h2d, int(y_pins[0].numel() * 2)
+    return ms, h2d, int(y_pins[0].numel() * 2), ms_copy
 
 
 def run_brackets(ctx, case, steps):
@@ -517,7 +535,7 @@ def main():
                     steps=args.steps, warmup=args.warmup)
     br = run_brackets(ctx, case, min(args.steps, 16))
     clocks = sampler.stop()
-    ms_e2e, h2d, d2h = run_e2e(ctx, case, args.steps, args.warmup)
+    ms_e2e, h2d, d2h, ms_copy = run_e2e(ctx, case, args.steps, args.warmup)
     it = case["_internal"]
     shape, S, cfg = it["shape"], it["S"], it["cfg"]
     H, I, K = shape.hidden, shape.ffn_hidden, shape.topk
@@ -556,7 +574,7 @@ def main():
         "parity": case["parity"],
         "capacity_redos": case["capacity_redos"],
         "e2e": {"value": flops_step / (ms_e2e * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_e2e,
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "copies_alone_ms_per_step": ms_copy,
                 "pipelined": "inputs of step i+1 and the output of step i-1 are copied on side streams during step i"},
         "gpu_launches": int(round(case["gpu_launches_per_step"] * args.steps)),
         "roofline": {"bound": "hbm", "kernel": "moe_gemm_kernel<gate|up + SwiGLU> (dispatch GEMM)", "achieved": achieved,

@@ -19,6 +19,9 @@ def build(force=False, verbose=False):
            "-Xcompiler", "-fPIC", "-o", OUT, SRC]
     if verbose:
         cmd[1:1] = ["-Xptxas", "-v"]
+    extra = os.environ.get("ZEPP_B200_NVCC_FLAGS", "").split()     # e.g. -DZEPP_FINE_TRACE, -DZEPP_GEMM_PROFILE
+    if extra:
+        cmd[1:1] = extra
     subprocess.run(cmd, check=True)
     return OUT
 

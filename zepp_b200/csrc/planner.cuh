@@ -55,12 +55,9 @@ __device__ __forceinline__ unsigned long long step_epoch(const unsigned long lon
 // (python/zepp/planner.py:104-112: index_add_ + all_gather_into_tensor).
 // One block.  dst.ptr[p] is rank p's loads table [R, G]; flags.ptr[p] its arrival words [R].
 // ---------------------------------------------------------------------------------------
-__global__ void loads_publish_kernel(const int* __restrict__ topk_own, int n_entries, int G, int rank, int world,
-                                     PeerTable dst0, PeerTable dst1, PeerTable flags, unsigned long long* ctr,
-                                     unsigned long long* status, long long* route_stats) {
-  extern __shared__ int hist[];
-  const unsigned long long epoch = step_epoch(ctr, true);      // first kernel of a step
-  const PeerTable& dst = (epoch & 1) ? dst1 : dst0;
+__device__ __forceinline__ void loads_publish_block(const int* __restrict__ topk_own, int n_entries, int G, int rank, int world,
+                                                    const PeerTable& dst, const PeerTable& flags, unsigned long long epoch,
+                                                    unsigned long long* status, long long* route_stats, int* hist) {
   if (threadIdx.x == 0) trace_mark(status, TR_LOADS);
   if (route_stats != nullptr && threadIdx.x < 4) route_stats[threadIdx.x] = 0;
   for (int g = threadIdx.x; g < G; g += blockDim.x) hist[g] = 0;
@@ -79,6 +76,14 @@ __global__ void loads_publish_kernel(const int* __restrict__ topk_own, int n_ent
   __syncthreads();
   if (threadIdx.x < world && flags.ptr[threadIdx.x] != nullptr)
     st_relaxed_sys(reinterpret_cast<unsigned long long*>(flags.ptr[threadIdx.x]) + rank, epoch);
+}
+
+__global__ void loads_publish_kernel(const int* __restrict__ topk_own, int n_entries, int G, int rank, int world,
+                                     PeerTable dst0, PeerTable dst1, PeerTable flags, unsigned long long* ctr,
+                                     unsigned long long* status, long long* route_stats) {
+  extern __shared__ int hist[];
+  const unsigned long long epoch = step_epoch(ctr, true);      // first kernel of a step
+  loads_publish_block(topk_own, n_entries, G, rank, world, (epoch & 1) ? dst1 : dst0, flags, epoch, status, route_stats, hist);
   if (threadIdx.x == 0 && ctr != nullptr) *ctr = epoch;
 }
 

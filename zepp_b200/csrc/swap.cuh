@@ -30,6 +30,7 @@ struct SwapArgs {
   int* slot_of;         // [G] out: the first valid l2p entry of every expert on the placement this step routes on
   int rank;
   int* sched;           // [gpe] out: schedule word per local group (bit 30 = slot received an expert this step)
+  int first;            // the calling kernel is the step's first: the epoch is *epoch_ptr + 1 (not committed yet)
   int* redirect;        // [gpe] out: group whose weights the GEMMs read: the group itself, or gpe + i for the i-th incoming expert
   unsigned int* ready;  // [2 * cap] out: zeroed chunk counters of the staging entries (W1, then W2)
 };
@@ -78,8 +79,8 @@ __device__ void swap_step_tables(const SwapArgs& a, const int* cur, int cnt, con
   }
 }
 
-__global__ void __launch_bounds__(kSwapThreads) swap_decide_kernel(SwapArgs a) {
-  extern __shared__ long long sm64[];
+// The decision by one block of any size (shared memory: swap_decide_smem_bytes for that size).
+__device__ void swap_decide_body(SwapArgs a, long long* sm64) {
   const int R = a.R, G = a.G, L = a.L, nlp = a.nlp, NS = R * nlp, NN = R / L, P = L / 2, Q = NN * P;
   long long* lg = sm64;                 // [G]
   long long* w = lg + G;                // [NS]
@@ -95,7 +96,7 @@ __global__ void __launch_bounds__(kSwapThreads) swap_decide_kernel(SwapArgs a) {
   const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, wid = tid >> 5, nw = nt >> 5;
   const int off_cnt = 3, off_mv = 3 + R, off_p2l = off_mv + 4 * R * a.cap, off_lg = off_p2l + NS;
   if (a.epoch_ptr != nullptr) {
-    const unsigned long long epoch = step_epoch(a.epoch_ptr, false);
+    const unsigned long long epoch = step_epoch(a.epoch_ptr, a.first != 0);
     if (epoch & 1) a.loads = a.loads_odd;
     if (tid == 0) trace_mark(a.status, TR_DECIDE);
     if (!block_wait_all(a.loads_flags, R, epoch, a.limit_ns, a.status, WAIT_LOADS)) return;
@@ -306,6 +307,16 @@ __global__ void __launch_bounds__(kSwapThreads) swap_decide_kernel(SwapArgs a) {
     const int cnt = a.sched != nullptr ? min((int)a.out[off_cnt + a.rank], a.cap) : 0;
     swap_step_tables(a, cur, cnt, a.out + off_mv + (size_t)a.rank * a.cap * 4);
   }
+}
+
+__global__ void __launch_bounds__(kSwapThreads) swap_decide_kernel(SwapArgs a) {
+  extern __shared__ long long swap_sm64[];
+  swap_decide_body(a, swap_sm64);
+}
+
+__host__ __device__ inline size_t swap_decide_smem_bytes(int R, int G, int L, int nlp, int threads) {
+  const int NS = R * nlp, NN = R / L, Q = NN * (L / 2) > 0 ? NN * (L / 2) : 1;
+  return (size_t)(G + NS + R) * 8 + (size_t)(2 * NS + 7 * Q + NN + (threads / 32) * 16 + 8) * 4;
 }
 
 // Swap-lane metadata of one rank from the decision's result block: gate words of the unchanged
