@@ -32,7 +32,7 @@ sys.path.insert(0, ROOT)
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one dispatch-GEMM launch from an ncu capture of the same
 # command, keyed by (workload, GPUs, tokens per rank)
-NCU_TRAFFIC = {("qwen3-30b", 1, 512): 849.7e6}
+NCU_TRAFFIC = {("qwen3-235b", 1, 512): 3310.6e6, ("qwen3-30b", 1, 512): 848.3e6}
 METRIC = "moe_layer_tflops"
 UNIT = "TFLOP/s"
 NVLINK_BPS = 900e9            # per direction per GPU: the figure the roofline is defined with
@@ -278,7 +278,7 @@ def run_case(ctx, args, workload, strategy, tokens=None, swap=None, drift_steps=
     redos0 = layer.redos
     for attempt in range(4):
         try:
-            for i in range(max(n_batches, warmup)):
+            for i in range(max(n_batches, warmup, n_x)):          # every (batch, x buffer) pair: all step graphs captured
                 step_resident(i)
                 if i < n_batches:
                     layer.check()           # the verdict of every distinct batch (a later step overwrites the mask)

@@ -85,3 +85,22 @@ def test_workload_generators_are_seeded(config_cases):
     q = wl.drift(p, 0.1, g)
     assert torch.allclose(q.sort().values, p.sort().values) and int((q != p).sum()) <= 13
     assert wl.expert_w1(3, shape).shape == (3072, 4096) and wl.expert_w2(3, shape).shape == (4096, 1536)
+
+
+def test_token_buckets_follow_the_serving_rule():
+    """k, 2k, 4k, ... and max_tokens_per_rank itself (python/zepp/serving.py:42-50), also when the maximum is no power of two."""
+    from zepp_b200 import token_buckets
+    shape = ModelShape(16, 4, 256, 128, act="swiglu")
+    mk = lambda s: EPMoEConfig(shape=shape, ranks=2, ranks_per_node=2, max_tokens_per_rank=s)  # noqa: E731
+    assert token_buckets(mk(4)) == [4]
+    assert token_buckets(mk(64)) == [4, 8, 16, 32, 64]
+    assert token_buckets(mk(40)) == [4, 8, 16, 32, 40]
+
+
+def test_grow_never_shrinks_and_keeps_the_aliased_buffers_together():
+    caps = Capacities(100, 100, 10, 10, 100, 10, 10, 50)
+    d = Demands(recv_rows=200, dispatch_recv=90, dispatch_stage=5, dispatch_relay=1, combine_conv=1, combine_wire=1, pair_rows=80)
+    g = grow(caps, d)
+    assert g.recv_cap == 300 and g.combine_send == 300 and g.dispatch_recv == 300
+    assert g.dispatch_stage == 10 and g.pair_cap == 50            # untouched where the demand fits / is not checked
+    assert grow(caps, d, direct=True).pair_cap == 120
