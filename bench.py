@@ -54,6 +54,7 @@ def parse():
     ap.add_argument("--swap", type=int, default=-1, help="expert swap on/off (default: the workload's setting)")
     ap.add_argument("--extra", type=int, default=-1, help="also run the other 8-GPU configurations (default: at 8 GPUs)")
     ap.add_argument("--sweep", type=int, default=0, help="decode / prefill sweep on the qwen3-235b shape")
+    ap.add_argument("--e2e-buffers", type=int, default=3, help="buffer sets of the end-to-end path (host copies in flight)")
     ap.add_argument("--parity-tokens", type=int, default=6, help="tokens of rank 0 checked against the CPU oracle")
     return ap.parse_args()
 
@@ -370,44 +371,63 @@ def run_case(ctx, args, workload, strategy, tokens=None, swap=None, drift_steps=
     return out
 
 
-def run_e2e(ctx, case, steps, warmup):
-    """The same steps through the public API with HOST buffers: every step copies its inputs from pinned host memory
-    and its output back.  Two buffer sets and two copy streams let the copies of neighbouring steps overlap the
-    compute of this one (each step still waits for its own inputs and delivers its own output)."""
+def run_e2e(ctx, case, steps, warmup, n_buf=3):
+    """The same steps through the public API with HOST buffers: every step copies its inputs (ids, gate weights, x: one
+    pinned block, one copy) from pinned host memory and its output back.  `n_buf` buffer sets and two copy streams let
+    the copies of neighbouring steps overlap the compute of this one (each step still waits for its own inputs and
+    delivers its own output)."""
     it = case["_internal"]
     layer, S, n_batches = it["layer"], it["S"], it["n_batches"]
     dev = ctx.dev
-    ids_pin = [t.pin_memory() for t in it["ids_host"]]
-    w_pin = [t.pin_memory() for t in it["w_host"]]
     xs_host = it["xs_host"]
     n_x = len(xs_host)
-    ids_in = [torch.empty_like(ids_pin[0], device=dev) for _ in range(2)]
-    w_in = [torch.empty_like(w_pin[0], device=dev) for _ in range(2)]
-    x_in = [torch.empty_like(xs_host[0], device=dev) for _ in range(2)]
-    y_dev = [torch.empty_like(x_in[0]) for _ in range(2)]
-    y_pins = [torch.empty_like(xs_host[0]).pin_memory() for _ in range(2)]
+    K = it["ids_host"][0].shape[1]
+    H = xs_host[0].shape[1]
+    n_ids, n_w, n_xb = S * K * 4, S * K * 4, S * H * 2
+    blob_bytes = n_ids + n_w + n_xb
+
+    def views(blob):
+        return (blob[:n_ids].view(torch.int32).view(S, K), blob[n_ids:n_ids + n_w].view(torch.float32).view(S, K),
+                blob[n_ids + n_w:].view(torch.bfloat16).view(S, H))
+
+    # host side: one pinned block per (batch, x buffer) pair the steps cycle through
+    n_host = n_batches * n_x // __import__("math").gcd(n_batches, n_x)
+    host_blobs = []
+    for i in range(n_host):
+        hb = torch.empty(blob_bytes, dtype=torch.uint8).pin_memory()
+        hi, hw, hx = views(hb)
+        hi.copy_(it["ids_host"][i % n_batches])
+        hw.copy_(it["w_host"][i % n_batches])
+        hx.copy_(xs_host[i % n_x])
+        host_blobs.append(hb)
+    dev_blobs = [torch.empty(blob_bytes, dtype=torch.uint8, device=dev) for _ in range(n_buf)]
+    dev_views = [views(b) for b in dev_blobs]
+    y_dev = [torch.empty(S, H, dtype=torch.bfloat16, device=dev) for _ in range(n_buf)]
+    y_pins = [torch.empty(S, H, dtype=torch.bfloat16).pin_memory() for _ in range(n_buf)]
     s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
-    ev_in = [torch.cuda.Event() for _ in range(2)]
-    ev_done = [torch.cuda.Event() for _ in range(2)]
+    ev_in = [torch.cuda.Event() for _ in range(n_buf)]
+    ev_done = [torch.cuda.Event() for _ in range(n_buf)]
+    ev_out = [torch.cuda.Event() for _ in range(n_buf)]
     main = torch.cuda.current_stream()
-    for e in ev_done:
+    for e in ev_done + ev_out:
         e.record(main)
 
     def step_e2e(i):
-        b = i & 1
+        b = i % n_buf
         with torch.cuda.stream(s_in):
-            s_in.wait_event(ev_done[b])               # step i-2 no longer reads this input set
-            ids_in[b].copy_(ids_pin[i % n_batches], non_blocking=True)
-            w_in[b].copy_(w_pin[i % n_batches], non_blocking=True)
-            x_in[b].copy_(xs_host[i % n_x], non_blocking=True)
+            s_in.wait_event(ev_done[b])               # the step that last used this input set has finished
+            dev_blobs[b].copy_(host_blobs[i % n_host], non_blocking=True)
             ev_in[b].record(s_in)
         main.wait_event(ev_in[b])
-        y = layer.step(ids_in[b], w_in[b], x_in[b])
+        main.wait_event(ev_out[b])                    # its output set has been read out
+        ids_b, w_b, x_b = dev_views[b]
+        y = layer.step(ids_b, w_b, x_b)
         y_dev[b].copy_(y, non_blocking=True)
         ev_done[b].record(main)
         with torch.cuda.stream(s_out):
             s_out.wait_event(ev_done[b])
             y_pins[b].copy_(y_dev[b], non_blocking=True)
+            ev_out[b].record(s_out)
 
     for i in range(max(3, warmup // 2)):
         step_e2e(i)
@@ -427,11 +447,9 @@ def run_e2e(ctx, case, steps, warmup):
     c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     c0.record()
     for i in range(steps):
-        b = i & 1
+        b = i % n_buf
         with torch.cuda.stream(s_in):
-            ids_in[b].copy_(ids_pin[i % n_batches], non_blocking=True)
-            w_in[b].copy_(w_pin[i % n_batches], non_blocking=True)
-            x_in[b].copy_(xs_host[i % n_x], non_blocking=True)
+            dev_blobs[b].copy_(host_blobs[i % n_host], non_blocking=True)
         with torch.cuda.stream(s_out):
             y_pins[b].copy_(y_dev[b], non_blocking=True)
     main.wait_stream(s_in)
@@ -439,8 +457,7 @@ def run_e2e(ctx, case, steps, warmup):
     c1.record()
     ctx.barrier()
     ms_copy = ctx.max_over_ranks(c0.elapsed_time(c1)) / steps
-    h2d = int(ids_pin[0].numel() * 4 + w_pin[0].numel() * 4 + xs_host[0].numel() * 2)
-    return ms, h2d, int(y_pins[0].numel() * 2), ms_copy
+    return ms, int(blob_bytes), int(y_pins[0].numel() * 2), ms_copy
 
 
 def run_brackets(ctx, case, steps):
@@ -535,7 +552,7 @@ def main():
                     steps=args.steps, warmup=args.warmup)
     br = run_brackets(ctx, case, min(args.steps, 16))
     clocks = sampler.stop()
-    ms_e2e, h2d, d2h, ms_copy = run_e2e(ctx, case, args.steps, args.warmup)
+    ms_e2e, h2d, d2h, ms_copy = run_e2e(ctx, case, args.steps, args.warmup, n_buf=args.e2e_buffers)
     it = case["_internal"]
     shape, S, cfg = it["shape"], it["S"], it["cfg"]
     H, I, K = shape.hidden, shape.ffn_hidden, shape.topk
@@ -575,7 +592,8 @@ def main():
         "capacity_redos": case["capacity_redos"],
         "e2e": {"value": flops_step / (ms_e2e * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "copies_alone_ms_per_step": ms_copy,
-                "pipelined": "inputs of step i+1 and the output of step i-1 are copied on side streams during step i"},
+                "pipelined": f"{args.e2e_buffers} buffer sets: inputs of later steps and outputs of earlier ones are copied on side "
+                             "streams during a step"},
         "gpu_launches": int(round(case["gpu_launches_per_step"] * args.steps)),
         "roofline": {"bound": "hbm", "kernel": "moe_gemm_kernel<gate|up + SwiGLU> (dispatch GEMM)", "achieved": achieved,
                      "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs, "peak_kind": peak_kind,

@@ -59,6 +59,7 @@ __global__ void __launch_bounds__(kMetaThreads) meta_fused_kernel(MetaArgs a, co
     }
     const int role = (int)blockIdx.x - n_tile_blocks - 1;
     if (role < f.n_route) {
+      #pragma unroll 1
       for (int g = threadIdx.x; g < f.route.G; g += blockDim.x) sm[g] = f.route.slot_of[g];
       __syncthreads();
       route_simple_rows(f.route, sm, role, f.n_route, epoch);
@@ -67,6 +68,7 @@ __global__ void __launch_bounds__(kMetaThreads) meta_fused_kernel(MetaArgs a, co
         __threadfence_system();
         if (atomicInc(f.route_counter, f.n_route - 1) == (unsigned int)f.n_route - 1) {
           __threadfence_system();
+          #pragma unroll 1
           for (int p = 0; p < f.route.world; ++p)
             st_relaxed_sys(reinterpret_cast<unsigned long long*>(f.route.flags.ptr[p]) + f.route.my_rank, epoch);
         }
@@ -95,6 +97,7 @@ __global__ void __launch_bounds__(kMetaThreads) meta_fused_kernel(MetaArgs a, co
   int my_v = -1;
   // ---- count
   if (!tables_block) {
+    #pragma unroll 1
     for (int i = threadIdx.x; i < E_virt + ucw; i += blockDim.x) sm[i] = 0;
     __syncthreads();
     if (valid) {
@@ -107,6 +110,7 @@ __global__ void __launch_bounds__(kMetaThreads) meta_fused_kernel(MetaArgs a, co
     const int t_cnt = min(a.S, t_lo + a.tokens_per_tile) - t_lo;
     if ((int)threadIdx.x < t_cnt) {
       unsigned long long owners = 0, nodes = 0;
+      #pragma unroll 1
       for (int k = 0; k < a.K; ++k) {
         const int v = s_v[threadIdx.x * a.K + k];
         if (v < 0) continue;
@@ -119,8 +123,10 @@ __global__ void __launch_bounds__(kMetaThreads) meta_fused_kernel(MetaArgs a, co
     }
     __syncthreads();
     int* th = a.tile_hist + (size_t)blockIdx.x * E_virt;
+    #pragma unroll 1
     for (int e = threadIdx.x; e < E_virt; e += blockDim.x) th[e] = hist[e];
     int* tu = a.tile_uc + (size_t)blockIdx.x * ucw;
+    #pragma unroll 1
     for (int i = threadIdx.x; i < ucw; i += blockDim.x) tu[i] = ucs[i];
   }
   // ---- grid barrier (every block of a cooperative launch is resident; the wait is bounded all the same)
@@ -161,10 +167,12 @@ __global__ void __launch_bounds__(kMetaThreads) meta_fused_kernel(MetaArgs a, co
     const int chunk = (n_tile_blocks + P - 1) / P;
     int* p_tot = wc;
     int* p_bef = wc + P * E_virt;
+    #pragma unroll 1
     for (int idx = threadIdx.x; idx < P * E_virt; idx += blockDim.x) {
       const int sl = idx / E_virt, e = idx - sl * E_virt;
       const int b_lo = sl * chunk, b_hi = min(n_tile_blocks, b_lo + chunk);
       int t = 0, b4 = 0;
+      #pragma unroll 4
       for (int b = b_lo; b < b_hi; ++b) {
         const int h = __ldcg(a.tile_hist + (size_t)b * E_virt + e);
         t += h;
@@ -174,8 +182,10 @@ __global__ void __launch_bounds__(kMetaThreads) meta_fused_kernel(MetaArgs a, co
       p_bef[idx] = b4;
     }
     __syncthreads();
+    #pragma unroll 1
     for (int e = threadIdx.x; e < E_virt; e += blockDim.x) {
       int t = 0, b4 = 0;
+      #pragma unroll 1
       for (int sl = 0; sl < P; ++sl) { t += p_tot[sl * E_virt + e]; b4 += p_bef[sl * E_virt + e]; }
       s_tot[e] = t;
       hist[e] = b4;
@@ -184,18 +194,22 @@ __global__ void __launch_bounds__(kMetaThreads) meta_fused_kernel(MetaArgs a, co
     const int per = (E_virt + blockDim.x - 1) / blockDim.x;
     const int lo = threadIdx.x * per;
     int mine = 0;
+    #pragma unroll 1
     for (int q = 0; q < per; ++q)
       if (lo + q < E_virt) mine += s_tot[lo + q];
     int total;
     int run = block_exclusive_scan(mine, s_warp_tot, &total);
+    #pragma unroll 1
     for (int q = 0; q < per; ++q)
       if (lo + q < E_virt) { s_base[lo + q] = run; run += s_tot[lo + q]; }
     if (threadIdx.x == 0) s_base[E_virt] = total;
     __syncthreads();
+    #pragma unroll 1
     for (int e = threadIdx.x; e < E_virt; e += blockDim.x) hist[e] += s_base[e];
   }
   // ---- rank: stable position of every copy inside its expert
   const int n_warps = (T + 31) / 32;
+  #pragma unroll 1
   for (int i = threadIdx.x; i < n_warps * E_virt; i += blockDim.x) wc[i] = 0;
   __syncthreads();
   const bool pad = valid && my_v < 0;
@@ -207,8 +221,10 @@ __global__ void __launch_bounds__(kMetaThreads) meta_fused_kernel(MetaArgs a, co
     if (my_v >= 0 && lane == __ffs(m) - 1) wc[wid * E_virt + e] = __popc(m);
   }
   __syncthreads();
+  #pragma unroll 1
   for (int x = threadIdx.x; x < E_virt; x += blockDim.x) {      // exclusive prefix over the tile's warps
     int run = hist[x];
+    #pragma unroll 1
     for (int w = 0; w < n_warps; ++w) {
       const int c = wc[w * E_virt + x];
       wc[w * E_virt + x] = run;
@@ -219,6 +235,7 @@ __global__ void __launch_bounds__(kMetaThreads) meta_fused_kernel(MetaArgs a, co
   if (a.staged && a.row_tok != nullptr) {
     // staging slot of a token on this rank = number of earlier tokens of its source that also come here
     const int tpt = a.tokens_per_tile;
+    #pragma unroll 1
     for (int t = threadIdx.x; t < tpt; t += blockDim.x) s_tokslot[t] = 0;
     __syncthreads();
     if (my_v >= 0 && my_v / a.gpe == a.my_rank) s_tokslot[threadIdx.x / a.K] = 1;
@@ -228,7 +245,9 @@ __global__ void __launch_bounds__(kMetaThreads) meta_fused_kernel(MetaArgs a, co
     int pre = block_exclusive_scan(f, s_warp_tot, &total);
     if (wid == 0) {                      // tokens of the source's earlier tiles that come here
       int acc = 0;
+      #pragma unroll 4
       for (int q = lane; q < tb; q += 32) acc += __ldcg(a.tile_uc + (size_t)(src * a.tiles_per_src + q) * ucw + a.my_rank);
+      #pragma unroll 1
       for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
       if (lane == 0) s_go = acc;
     }

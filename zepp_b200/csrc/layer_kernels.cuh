@@ -65,11 +65,14 @@ __device__ void push_block(const PushArgs& a, int blk, int nblk, unsigned long l
   const int tpb = (a.S + nblk - 1) / nblk;                    // tokens per block (<= kPushMaxTokensPerBlock)
   const int t_lo = min(a.S, blk * tpb);
   const int t_hi = min(a.S, t_lo + tpb);
+  #pragma unroll 1
   for (int d = threadIdx.x; d < a.world; d += blockDim.x) before[d] = 0;
   __syncthreads();
   // owner masks of all tokens below t_hi: count those before the range, keep those inside it
+  #pragma unroll 1
   for (int t = threadIdx.x; t < t_hi; t += blockDim.x) {
     unsigned long long m = 0;
+    #pragma unroll 8
     for (int k = 0; k < a.K; ++k) {
       int p;
       if (a.phys_own != nullptr) {
@@ -89,22 +92,27 @@ __device__ void push_block(const PushArgs& a, int blk, int nblk, unsigned long l
   __syncthreads();
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const int n_tok = t_hi - t_lo, n_words = (n_tok + 31) / 32;
+  #pragma unroll 1
   for (int w = wid; w < n_words; w += nw) {
     const unsigned long long m = 32 * w + lane < n_tok ? tmask[32 * w + lane] : 0ull;
+    #pragma unroll 1
     for (int d = 0; d < a.world; ++d) {
       const unsigned int bits = __ballot_sync(0xffffffffu, (m >> d) & 1ull);
       if (lane == 0) dbits[d][w] = bits;
     }
   }
   __syncthreads();
+  #pragma unroll 1
   for (int d = threadIdx.x; d < a.world; d += blockDim.x) {
     int run = before[d];
+    #pragma unroll 1
     for (int w = 0; w < n_words; ++w) { wpre[d][w] = run; run += __popc(dbits[d][w]); }
   }
   __syncthreads();
   // one warp per (token, destination) row
   const int vec_per_row = a.H / 8;
   const size_t region = (size_t)a.rank * a.region_tokens * a.H;
+  #pragma unroll 1
   for (int pair = wid; pair < (t_hi - t_lo) * a.world; pair += nw) {
     const int tl = pair / a.world, d = pair - tl * a.world;
     const unsigned long long m = tmask[tl];
@@ -112,6 +120,7 @@ __device__ void push_block(const PushArgs& a, int blk, int nblk, unsigned long l
     const int slot = wpre[d][tl >> 5] + __popc(dbits[d][tl >> 5] & ((1u << (tl & 31)) - 1u));
     const uint4* sp = reinterpret_cast<const uint4*>(a.x + (size_t)(t_lo + tl) * a.H);
     uint4* dp = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.stage.ptr[d]) + region + (size_t)slot * a.H);
+    #pragma unroll 1
     for (int v0 = 0; v0 < vec_per_row; v0 += 256) {
       uint4 buf[8];
 #pragma unroll
@@ -132,6 +141,7 @@ __device__ void push_block(const PushArgs& a, int blk, int nblk, unsigned long l
     const unsigned int prev = atomicInc(a.counter, nblk - 1);
     if (prev == (unsigned int)nblk - 1) {
       __threadfence_system();
+      #pragma unroll 1
       for (int p = 0; p < a.world; ++p)
         st_relaxed_sys(reinterpret_cast<unsigned long long*>(a.flags.ptr[p]) + a.rank, epoch);
     }

@@ -261,6 +261,7 @@ __device__ __forceinline__ long long region_rows(const int* uc, int W, int L, in
 __device__ __forceinline__ int block_exclusive_scan(int v, int* warp_tot, int* total) {
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   int incl = v;
+  #pragma unroll 1
   for (int off = 1; off < 32; off <<= 1) {
     const int u = __shfl_up_sync(0xffffffffu, incl, off);
     if (lane >= off) incl += u;
@@ -271,6 +272,7 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* warp_tot, int* t
   if (wid == 0) {
     const int t = lane < (int)(blockDim.x >> 5) ? warp_tot[lane] : 0;
     int inc2 = t;
+    #pragma unroll 1
     for (int off = 1; off < 32; off <<= 1) {
       const int u = __shfl_up_sync(0xffffffffu, inc2, off);
       if (lane >= off) inc2 += u;
@@ -301,11 +303,14 @@ __device__ void meta_scan_body(MetaArgs& a, int* sm, bool bases_in_place) {
   __shared__ long long viol;
   __syncthreads();
   if (threadIdx.x == 0) trace_mark(a.status, TR_SCAN);
+  #pragma unroll 1
   for (int i = threadIdx.x; i < R * R; i += blockDim.x) chunks[i] = 0;
+  #pragma unroll 1
   for (int e = threadIdx.x; e < E_virt; e += blockDim.x) s_splits[e] = 0;
   __syncthreads();
   // per source splits, totals, chunk table: one (source, expert) pair per thread, its tiles' counts loaded
   // independently of each other (the loop is unrolled so that the loads are in flight together)
+  #pragma unroll 1
   for (int idx = threadIdx.x; idx < R * E_virt; idx += blockDim.x) {
     const int s = idx / E_virt, e = idx - s * E_virt;
     const int* col = a.tile_hist + (size_t)s * a.tiles_per_src * E_virt + e;
@@ -318,6 +323,7 @@ __device__ void meta_scan_body(MetaArgs& a, int* sm, bool bases_in_place) {
       atomicAdd(&s_splits[e], acc);
     }
   }
+  #pragma unroll 1
   for (int i = threadIdx.x; i < R * ucw; i += blockDim.x) {
     const int s = i / ucw, d = i - s * ucw;
     const int* col = a.tile_uc + (size_t)s * a.tiles_per_src * ucw + d;
@@ -328,6 +334,7 @@ __device__ void meta_scan_body(MetaArgs& a, int* sm, bool bases_in_place) {
     s_uc[i] = acc;
   }
   __syncthreads();
+  #pragma unroll 1
   for (int e = threadIdx.x; e < E_virt; e += blockDim.x) a.splits[e] = s_splits[e];
   __syncthreads();
   if (threadIdx.x == 0) ZEPP_FINE_MARK(a.status, TR_SCAN_COUNTS);
@@ -336,10 +343,12 @@ __device__ void meta_scan_body(MetaArgs& a, int* sm, bool bases_in_place) {
     const int per = (E_virt + blockDim.x - 1) / blockDim.x;
     const int lo = threadIdx.x * per;
     int local = 0;
+    #pragma unroll 1
     for (int q = 0; q < per; ++q)
       if (lo + q < E_virt) local += s_splits[lo + q];
     int total;
     int run = block_exclusive_scan(local, warp_tot, &total);
+    #pragma unroll 1
     for (int q = 0; q < per; ++q)
       if (lo + q < E_virt) { a.expert_base[lo + q] = run; s_base[lo + q] = run; run += s_splits[lo + q]; }
     if (threadIdx.x == 0) { a.expert_base[E_virt] = total; s_base[E_virt] = total; }
@@ -347,8 +356,10 @@ __device__ void meta_scan_body(MetaArgs& a, int* sm, bool bases_in_place) {
   __syncthreads();
   if (threadIdx.x == 0) ZEPP_FINE_MARK(a.status, TR_SCAN_BASES);
   if (bases_in_place)
+  #pragma unroll 1
   for (int e = threadIdx.x; e < E_virt; e += blockDim.x) {      // tile histograms -> tile bases, in place
     int run = s_base[e];
+    #pragma unroll 1
     for (int b = 0; b < n_blocks; ++b) {
       const int h = a.tile_hist[(size_t)b * E_virt + e];
       a.tile_hist[(size_t)b * E_virt + e] = run;
@@ -359,6 +370,7 @@ __device__ void meta_scan_body(MetaArgs& a, int* sm, bool bases_in_place) {
     ZEPP_FINE_MARK(a.status, TR_SCAN_DEMANDS);
     long long out[8];
     demands_from_chunks(chunks, s_uc, R, a.L, a.relay_slots, a.direct, a.caps, out);
+    #pragma unroll 1
     for (int i = 0; i < 8; ++i) a.demands[i] = out[i];
     viol = out[7];
     if (a.status) {
@@ -388,6 +400,7 @@ __device__ void meta_scan_body(MetaArgs& a, int* sm, bool bases_in_place) {
     const int pre_late = block_exclusive_scan(late ? nt : 0, warp_tot, &tot_late);
     const int first = late ? tot_early + pre_late : pre_early;
     const int off = e < a.gpe ? s_base[g0 + (e < a.gpe ? e : 0)] - m_start : 0;
+    #pragma unroll 1
     for (int t = 0; t < nt; ++t) {
       const int slot = first + t;
       if (slot < a.max_tiles) {
@@ -420,11 +433,14 @@ __device__ void plan_heads(MetaArgs& a, const int* chunks, const int* s_uc) {
     const int W = R, L = a.L, rank = a.my_rank, me_n = rank / L, me_l = rank % L;
     const int nseg = L + NN - 1;
     long long err = 0, max_col = 0;
+    #pragma unroll 1
     for (int d = lane_w; d < W; d += 32) {
       long long col = 0;
+      #pragma unroll 1
       for (int s = 0; s < W; ++s) col += region_rows(s_uc, W, L, s, d);
       if (col > max_col) max_col = col;
     }
+    #pragma unroll 1
     for (int i = lane_w; i < W * W; i += 32) {
       const int s = i / W, d = i - s * W;
       const long long cv = chunks[i];
@@ -432,12 +448,15 @@ __device__ void plan_heads(MetaArgs& a, const int* chunks, const int* s_uc) {
       if (!(uv >= 0 && uv <= cv && ((uv > 0) == (cv > 0)))) err |= 4;
       if (uv > s_uc[s * ucw + W + d / L]) err |= 8;
     }
+    #pragma unroll 1
     for (int i = lane_w; i < W * NN; i += 32) {
       const int s = i / NN, n = i - s * NN;
       long long su = 0;
+      #pragma unroll 1
       for (int l = 0; l < L; ++l) su += s_uc[s * ucw + n * L + l];
       if (s_uc[s * ucw + W + n] > su) err |= 8;
     }
+    #pragma unroll 1
     for (int o = 16; o > 0; o >>= 1) {
       err |= __shfl_xor_sync(0xffffffffu, err, o);
       const long long m2 = __shfl_xor_sync(0xffffffffu, max_col, o);
@@ -447,8 +466,10 @@ __device__ void plan_heads(MetaArgs& a, const int* chunks, const int* s_uc) {
       long long seg = 0;
       int si = 0;
       seg_tab[0] = 0;
+      #pragma unroll 1
       for (int n = 0; n < NN; ++n) {
         if (n == me_n) {
+          #pragma unroll 1
           for (int dl = 0; dl < L; ++dl) { seg += s_uc[rank * ucw + n * L + dl]; seg_tab[++si] = seg; }
         } else {
           seg += s_uc[rank * ucw + W + n];
@@ -458,11 +479,14 @@ __device__ void plan_heads(MetaArgs& a, const int* chunks, const int* s_uc) {
     }
     __syncwarp();
     long long* P = a.dplan;
+    #pragma unroll 1
     for (int i = lane_w; i <= nseg; i += 32) P[8 + i] = seg_tab[i];
     const int r0 = 8 + nseg + 1;
+    #pragma unroll 1
     for (int dl = lane_w; dl < L; dl += 32) {
       const int d = me_n * L + dl;
       long long off = 0;
+      #pragma unroll 1
       for (int s = 0; s < rank; ++s) off += region_rows(s_uc, W, L, s, d);
       P[r0 + 3 * dl + 0] = s_uc[rank * ucw + d];
       P[r0 + 3 * dl + 1] = seg_tab[me_n + dl];
@@ -472,7 +496,9 @@ __device__ void plan_heads(MetaArgs& a, const int* chunks, const int* s_uc) {
       if (max_col > a.caps[1]) err |= 16;
       if (seg_tab[nseg] > a.copies_per_rank) err |= 32;
       long long m0 = 0, off_me = 0;
+      #pragma unroll 1
       for (int s = 0; s < W; ++s) m0 += chunks[s * W + rank];
+      #pragma unroll 1
       for (int s = 0; s < rank; ++s) off_me += region_rows(s_uc, W, L, s, rank);
       P[0] = m0; P[1] = seg_tab[nseg]; P[2] = s_uc[rank * ucw + rank]; P[3] = seg_tab[me_n + me_l]; P[4] = off_me;
       P[5] = err; P[6] = 0; P[7] = 0;
@@ -485,20 +511,24 @@ __device__ void plan_heads(MetaArgs& a, const int* chunks, const int* s_uc) {
     long long* sr = so + W + 1;
     long long* dof = sr + W;
     long long* lo = dof + W;
+    #pragma unroll 1
     for (int d = lane_w; d < W; d += 32) {
       sr[d] = chunks[d * W + rank];
       long long before = 0;
+      #pragma unroll 1
       for (int s = 0; s < rank; ++s) before += chunks[d * W + s];
       dof[d] = before;
     }
     if (lane_w == 0) {
       long long acc = 0;
       so[0] = 0;
+      #pragma unroll 1
       for (int d = 0; d < W; ++d) { acc += chunks[d * W + rank]; so[d + 1] = acc; }
     }
     if (lane_w == 1) {
       long long acc = 0;
       lo[0] = 0;
+      #pragma unroll 1
       for (int s = 0; s < W; ++s) { acc += chunks[rank * W + s]; lo[s + 1] = acc; }
     }
   }

@@ -60,16 +60,20 @@ __device__ __forceinline__ void loads_publish_block(const int* __restrict__ topk
                                                     unsigned long long* status, long long* route_stats, int* hist) {
   if (threadIdx.x == 0) trace_mark(status, TR_LOADS);
   if (route_stats != nullptr && threadIdx.x < 4) route_stats[threadIdx.x] = 0;
+  #pragma unroll 1
   for (int g = threadIdx.x; g < G; g += blockDim.x) hist[g] = 0;
   __syncthreads();
+  #pragma unroll 1
   for (int n = threadIdx.x; n < n_entries; n += blockDim.x) {
     const int g = topk_own[n];
     if (g >= 0 && g < G) atomicAdd(&hist[g], 1);
     else if (g >= G && status) atomicOr(status + ST_ERROR, (unsigned long long)ERR_BAD_INDEX);   // negative: a pad copy
   }
   __syncthreads();
+  #pragma unroll 1
   for (int p = 0; p < world; ++p) {
     int* row = reinterpret_cast<int*>(dst.ptr[p]) + (size_t)rank * G;
+    #pragma unroll 1
     for (int g = threadIdx.x; g < G; g += blockDim.x) row[g] = hist[g];
   }
   __threadfence_system();
@@ -526,6 +530,7 @@ __device__ void route_simple_rows(const SimpleRouteArgs& a, const int* slots, in
   const size_t row_off = (size_t)a.my_rank * 2 * SK;
   if ((SK & 3) == 0) {
     // four entries per thread, 16-byte stores into every rank's gather table
+    #pragma unroll 1
     for (int q = blk * blockDim.x + threadIdx.x; q < SK / 4; q += nblk * blockDim.x) {
       const int4 e4 = reinterpret_cast<const int4*>(a.topk_own)[q];
       const int4 w4 = reinterpret_cast<const int4*>(wbits)[q];
@@ -539,6 +544,7 @@ __device__ void route_simple_rows(const SimpleRouteArgs& a, const int* slots, in
         reinterpret_cast<int4*>(a.send_row)[q] = p4;
         reinterpret_cast<int4*>(a.send_row + SK)[q] = w4;
       }
+      #pragma unroll 1
       for (int p = 0; p < a.world; ++p) {
         int* row = reinterpret_cast<int*>(dst.ptr[p]) + row_off;
         reinterpret_cast<int4*>(row)[q] = p4;
@@ -546,11 +552,13 @@ __device__ void route_simple_rows(const SimpleRouteArgs& a, const int* slots, in
       }
     }
   } else {
+    #pragma unroll 1
     for (int n = blk * blockDim.x + threadIdx.x; n < SK; n += nblk * blockDim.x) {
       const int p0 = single_replica_slot(a, slots, a.topk_own[n]);
       const int wb = wbits[n];
       a.phys_own[n] = p0;
       if (a.send_row) { a.send_row[n] = p0; a.send_row[SK + n] = wb; }
+      #pragma unroll 1
       for (int p = 0; p < a.world; ++p) {
         int* row = reinterpret_cast<int*>(dst.ptr[p]) + row_off;
         row[n] = p0;

@@ -58,8 +58,10 @@ __device__ __forceinline__ void slot_key(const int* cur, const long long* w, int
 __device__ void swap_step_tables(const SwapArgs& a, const int* cur, int cnt, const long long* mv) {
   const int NS = a.R * a.nlp, gpe = a.nlp + 1;
   if (a.slot_of != nullptr) {
+    #pragma unroll 1
     for (int e = threadIdx.x; e < a.G; e += blockDim.x) {
       int p0 = -1;
+      #pragma unroll 1
       for (int s = 0; s < NS && p0 < 0; ++s)
         if (cur[s] == e) p0 = s;
       a.slot_of[e] = p0;
@@ -67,10 +69,13 @@ __device__ void swap_step_tables(const SwapArgs& a, const int* cur, int cnt, con
   }
   if (threadIdx.x == 0 && a.epoch_ptr != nullptr) trace_mark(a.status, TR_DECIDE_END);
   if (a.ready != nullptr)
+    #pragma unroll 1
     for (int i = threadIdx.x; i < 2 * a.cap; i += blockDim.x) a.ready[i] = 0u;
   if (a.sched != nullptr) {
+    #pragma unroll 1
     for (int g = threadIdx.x; g < gpe; g += blockDim.x) {
       int hit = -1;
+      #pragma unroll 1
       for (int i = 0; i < cnt; ++i)
         if ((int)mv[4 * i] == g - 1) hit = i;
       a.sched[g] = hit >= 0 ? (1 << 30) : 0;
@@ -103,13 +108,17 @@ __device__ void swap_decide_body(SwapArgs a, long long* sm64) {
     if (tid == 0) trace_mark(a.status, TR_DECIDE_GO);
   }
 
+  #pragma unroll 1
   for (int e = tid; e < G; e += nt) {
     long long s = 0;
+    #pragma unroll 4
     for (int r = 0; r < R; ++r) s += a.loads[r * G + e];
     lg[e] = s;
   }
+  #pragma unroll 1
   for (int s = tid; s < NS; s += nt) { a0[s] = a.p2l[s]; cur[s] = a0[s]; }
   __syncthreads();
+  #pragma unroll 1
   for (int s = tid; s < NS; s += nt) {
     const int e = a0[s];
     long long lc = e >= 0 ? a.lcnts[e] : 1;
@@ -117,26 +126,34 @@ __device__ void swap_decide_body(SwapArgs a, long long* sm64) {
     w[s] = e >= 0 ? lg[e] / lc : 0;
   }
   __syncthreads();
+  #pragma unroll 1
   for (int r = tid; r < R; r += nt) {
     long long s = 0;
+    #pragma unroll 1
     for (int j = 0; j < nlp; ++j) s += w[r * nlp + j];
     Lr[r] = s;
   }
   if (tid == 0) { s_any = 0; s_stop = 0; s_rounds = 0; }
   __syncthreads();
+  #pragma unroll 1
   for (int n = tid; n < NN; n += nt) {
     node_out[n] = band_out(Lr, n, L, a.C) ? 1 : 0;
     if (node_out[n]) atomicOr(&s_any, 1);
   }
   __syncthreads();
+  #pragma unroll 1
   for (int e = tid; e < G; e += nt) a.out[off_lg + e] = lg[e];
 
   if (s_any && Q > 0 && L <= kSwapMaxL) {
+    #pragma unroll 1
     for (int round = 0; round < a.max_rounds; ++round) {
       // pairs: k-th heaviest with k-th lightest rank of every node (stable by key -Lr*L + l)
+      #pragma unroll 1
       for (int n = tid; n < NN; n += nt) {
         int ord[kSwapMaxL];
+        #pragma unroll 1
         for (int l = 0; l < L; ++l) ord[l] = l;
+        #pragma unroll 1
         for (int i = 1; i < L; ++i) {
           const int v = ord[i];
           const long long kv = -Lr[n * L + v] * L + v;
@@ -144,9 +161,11 @@ __device__ void swap_decide_body(SwapArgs a, long long* sm64) {
           while (j >= 0 && (-Lr[n * L + ord[j]] * L + ord[j]) > kv) { ord[j + 1] = ord[j]; --j; }
           ord[j + 1] = v;
         }
+        #pragma unroll 1
         for (int q = 0; q < P; ++q) { Hh[n * P + q] = n * L + ord[q]; Lo[n * P + q] = n * L + ord[L - 1 - q]; }
       }
       __syncthreads();
+      #pragma unroll 1
       for (int q = wid; q < Q; q += nw) {
         const int h = Hh[q], lo = Lo[q];
         const long long LH = Lr[h], LL = Lr[lo];
@@ -155,12 +174,15 @@ __device__ void swap_decide_body(SwapArgs a, long long* sm64) {
         const int Kc = nlp < 8 ? nlp : 8;
         bool pair_ok = (LH - LL > 1) && node_out[h / L];
         if (pair_ok) {
+          #pragma unroll 1
           for (int side = 0; side < 2; ++side) {
             const int base = (side == 0 ? h : lo) * nlp;
+            #pragma unroll 1
             for (int t = lane; t < nlp; t += 32) {
               long long k1, k2;
               slot_key(cur, w, base + t, side == 0, k1, k2);
               int rank = 0;
+              #pragma unroll 1
               for (int u = 0; u < nlp; ++u) {
                 long long u1, u2;
                 slot_key(cur, w, base + u, side == 0, u1, u2);
@@ -174,12 +196,14 @@ __device__ void swap_decide_body(SwapArgs a, long long* sm64) {
         long long best = -kSwapBig;
         int best_idx = -1;
         if (pair_ok) {
+          #pragma unroll 1
           for (int idx = lane; idx < Kc * Kc; idx += 32) {
             const int sh = ch[idx / Kc], sl = cl[idx % Kc];
             const int eh = cur[sh], el = cur[sl];
             const long long wh = w[sh], wl = w[sl];
             bool ok = eh >= 0 && el >= 0 && eh != el && wh > wl;
             if (ok) {
+              #pragma unroll 1
               for (int u = 0; u < nlp; ++u)
                 if (cur[lo * nlp + u] == eh || cur[h * nlp + u] == el) { ok = false; break; }
             }
@@ -193,6 +217,7 @@ __device__ void swap_decide_body(SwapArgs a, long long* sm64) {
             }
           }
         }
+        #pragma unroll 1
         for (int o = 16; o > 0; o >>= 1) {
           const long long ob = __shfl_xor_sync(0xffffffffu, best, o);
           const int oi = __shfl_xor_sync(0xffffffffu, best_idx, o);
@@ -211,17 +236,21 @@ __device__ void swap_decide_body(SwapArgs a, long long* sm64) {
       __syncthreads();
       if (tid == 0) {
         int n_sw = 0;
+        #pragma unroll 1
         for (int q = 0; q < Q; ++q) n_sw += sw[5 * q];
         if (n_sw == 0) {
           s_stop = 1;
         } else {
           // changed slots per rank against the step's original placement, with the round applied
           bool over = false;
+          #pragma unroll 1
           for (int r = 0; r < R && !over; ++r) {
             int changed = 0;
+            #pragma unroll 1
             for (int j = 0; j < nlp; ++j) {
               const int s = r * nlp + j;
               int v = cur[s];
+              #pragma unroll 1
               for (int q = 0; q < Q; ++q) {
                 if (!sw[5 * q]) continue;
                 if (sw[5 * q + 1] == s) v = sw[5 * q + 4];
@@ -234,14 +263,17 @@ __device__ void swap_decide_body(SwapArgs a, long long* sm64) {
           if (over) {
             s_stop = 1;
           } else {
+            #pragma unroll 1
             for (int q = 0; q < Q; ++q) {
               if (!sw[5 * q]) continue;
               cur[sw[5 * q + 1]] = sw[5 * q + 4];
               cur[sw[5 * q + 3]] = sw[5 * q + 2];
             }
             s_rounds += 1;
+            #pragma unroll 1
             for (int q = 0; q < Q; ++q) {
               if (!sw[5 * q]) continue;
+              #pragma unroll 1
               for (int z = 0; z < 2; ++z) {
                 const int sx = sw[5 * q + (z == 0 ? 1 : 3)];
                 const int e = cur[sx];
@@ -252,6 +284,7 @@ __device__ void swap_decide_body(SwapArgs a, long long* sm64) {
                 w[sx] = wn;
               }
             }
+            #pragma unroll 1
             for (int n = 0; n < NN; ++n) node_out[n] = band_out(Lr, n, L, a.C) ? 1 : 0;
           }
         }
@@ -264,28 +297,37 @@ __device__ void swap_decide_body(SwapArgs a, long long* sm64) {
   const int rounds = s_rounds;
   if (rounds == 0) {
     if (tid == 0) { a.out[0] = 0; a.out[1] = 0; a.out[2] = 0; }
+    #pragma unroll 1
     for (int r = tid; r < R; r += nt) a.out[off_cnt + r] = 0;
+    #pragma unroll 1
     for (int s = tid; s < NS; s += nt) a.out[off_p2l + s] = a0[s];
     swap_step_tables(a, cur, 0, nullptr);
     return;
   }
+  #pragma unroll 1
   for (int s = tid; s < NS; s += nt) { a.out[off_p2l + s] = cur[s]; a.p2l[s] = cur[s]; }
+  #pragma unroll 1
   for (int e = tid; e < G; e += nt) {          // l2p: slots of every expert, ascending
     int j = 0;
+    #pragma unroll 1
     for (int s = 0; s < NS; ++s)
       if (cur[s] == e && j < R) a.l2p[e * R + j++] = s;
+    #pragma unroll 1
     for (; j < R; ++j) a.l2p[e * R + j] = -1;
   }
   __shared__ int s_total, s_err;
   if (tid == 0) { s_total = 0; s_err = 0; }
   __syncthreads();
+  #pragma unroll 1
   for (int r = tid; r < R; r += nt) {          // pull lists, sorted by destination slot
     int cnt = 0;
     const int node = r / L;
+    #pragma unroll 1
     for (int j = 0; j < nlp; ++j) {
       const int e = cur[r * nlp + j];
       if (e < 0 || a0[r * nlp + j] == e) continue;
       int sr = -1, ss = -1;
+      #pragma unroll 1
       for (int s = node * L * nlp; s < (node + 1) * L * nlp; ++s)
         if (a0[s] == e) { sr = s / nlp; ss = s % nlp; }
       if (cnt < a.cap && sr >= 0) {
