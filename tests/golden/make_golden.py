@@ -2,7 +2,7 @@
 
 Run in a container where the reference checkout is mounted:
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 The reference's `zepp` package imports a compiled NVSHMEM extension at import time; only its pure
 Python planner is needed here, so `zepp._ext` is replaced by an empty stub before the import.
@@ -170,7 +170,9 @@ def config_case(mods, name, W, L, G, K, S, zipf_s, C, with_swap, seed=0):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: python %s <checkout of the reference project>" % sys.argv[0])
+    root = sys.argv[1]
     mods = load_reference(root)
     gen = torch.Generator().manual_seed(1)
     cases = {}

@@ -1,7 +1,7 @@
 """Generates tests/golden/layer_cases.npz: outputs of the reference's own layer check code on small
 seeded inputs, to pin oracle/layer.py.
 
-    python tests/golden/make_layer_golden.py [/path/to/reference]
+    python tests/golden/make_layer_golden.py /path/to/reference
 
 * `y_fp32`  = examples/serving_check.py `reference(x, ids, w, W1, W2, shape)` run as it is (CPU tensors).
 * `y_bf16`  = the loop of bench/replay.py `torch_reference` (which is written for CUDA tensors) re-run here on
@@ -51,7 +51,9 @@ def bf16_loop(activation, x, ids, probs, W1, W2, shape):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: python %s <checkout of the reference project>" % sys.argv[0])
+    root = sys.argv[1]
     zepp, activation, chk = load(root)
     out = {}
     cases = [(16, 4, 64, 32, 24, 1), (32, 8, 64, 32, 40, 2), (8, 2, 128, 64, 17, 3)]

@@ -1,7 +1,7 @@
 """Generates tests/golden/traces/ (a synthetic stand-in trace directory) and tests/golden/trace_cases.json
 (what the reference's own sampler, bench/traces.py, returns on that directory).
 
-    python tests/golden/make_trace_golden.py [/path/to/reference]
+    python tests/golden/make_trace_golden.py /path/to/reference
 
 The reference's trace files themselves are not copied; as a cross-check the script also runs this
 package's sampler on them where they lie and records whether it reproduces the batch hashes the
@@ -23,7 +23,9 @@ KEYS = [("qwen3", 16, 4, 1, 8192), ("qwen3", 8, 8, 4, 8192), ("qwen3", 8, 8, 0.5
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: python %s <checkout of the reference project>" % sys.argv[0])
+    root = sys.argv[1]
     spec = importlib.util.spec_from_file_location("ref_traces", os.path.join(root, "bench", "traces.py"))
     ref = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(ref)
