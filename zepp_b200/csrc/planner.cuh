@@ -327,7 +327,7 @@ __global__ void __launch_bounds__(256) route_kernel(RouteArgs a) {
 
 // ---------------------------------------------------------------------------------------
 // vacate + routing exchange.
-// route_vacate_kernel: one thread runs the per-token vacate pass of this source in token order
+// route_vacate_kernel: one warp runs the per-token vacate pass of this source in token order
 // with the host reference's semantics (python/zepp/routing.py:242-297: least-touched remote node
 // first, targets = home then the other touched nodes in first-touch order, all-or-nothing per
 // node, budgets paid on both replicas); launched only when the topology has more than one node.
@@ -439,8 +439,197 @@ __device__ void vacate_serial(const FinishArgs& a) {
   if (a.stats) a.stats[1] = moves;
 }
 
-__global__ void route_vacate_kernel(FinishArgs a) {
-  if (blockIdx.x == 0 && threadIdx.x == 0) vacate_serial(a);
+// The same pass run by a block of warps, a lane per entry of a token (K <= 32).  The budgets are shared state, so
+// tokens take effect in token order; but a token that cannot vacate any node changes nothing.  The block therefore
+// looks at kVacWarps consecutive tokens at once, one warp each, against the budgets as they stand; tokens before
+// the first one that can move are finished, that one runs its whole pass (it alone writes), and the block goes on
+// behind it.  Within a token the group counts, the candidate choice and every entry's plan are warp operations;
+// the budget tables sit in shared memory when they fit (`staged`), the token rows are staged `chunk` tokens at a
+// time.  Results equal vacate_serial's bit for bit: a token's plan reads the budgets before any of its entries is
+// applied, and the applies are atomic adds, which commute.
+constexpr int kVacWarps = 16;
+
+struct VacateShape {
+  int staged;      // 1: rel | ext | (rphys | rep << 24) | c tables live in dynamic shared memory
+  int chunk;       // tokens staged per round
+  size_t smem;     // dynamic shared memory bytes of the launch
+};
+
+inline VacateShape vacate_shape(int G, int R, int K, int nlp, bool tables_in_global = false) {
+  VacateShape v{};
+  const size_t limit = 44 * 1024;
+  const size_t tables = ((size_t)3 * G * route_cm(R) + G) * sizeof(int);
+  const size_t row = (size_t)2 * (K < 1 ? 1 : K) * sizeof(int);
+  v.staged = (!tables_in_global && tables + 8 * row <= limit && (long long)R * nlp < (1ll << 24)) ? 1 : 0;
+  const size_t left = limit - (v.staged ? tables : 0);
+  size_t chunk = left / row;
+  if (chunk > 256) chunk = 256;
+  v.chunk = (int)chunk;
+  v.smem = (v.staged ? tables : 0) + chunk * row;
+  return v;
+}
+
+struct VacateTabs {
+  int* rel;              // budgets (shared or global)
+  int* ext;
+  const int* pk;         // staged: rphys | rep << 24 (else nullptr)
+  const int* rep;        // global tables
+  const int* rphys;
+  const int* cc;         // replicas per expert
+  int CM, L, nlp, home, K;
+};
+
+// One token, one warp.  dry: return true as soon as some node could be vacated, change nothing.
+// Otherwise run the token's whole pass, write its row back and return the number of entries moved.
+__device__ int vacate_token(const VacateTabs& v, int* row_ph, const int* row_tk, int* grp_node, bool dry) {
+  const int lane = threadIdx.x & 31;
+  const int K = v.K, L = v.L, CM = v.CM, home = v.home;
+  // budgets are read where the atomics that change them land (never from a stale L1 line of the global tables)
+  auto budget = [](const int* p) { return *reinterpret_cast<const volatile int*>(p); };
+  const bool active = lane < K;
+  int ph = active ? row_ph[lane] : -1;
+  const int g = active ? row_tk[lane] : -1;
+  int node = ph < 0 ? home : ph / v.nlp / L;          // a pad copy is never remote
+  if (__ballot_sync(0xffffffffu, node != home) == 0) return 0;
+  int moves = 0;
+  for (int guard = 0; guard < 4 * K + 4; ++guard) {
+    const bool is_remote = node != home;
+    if (__ballot_sync(0xffffffffu, is_remote) == 0) break;
+    const unsigned peers = __match_any_sync(0xffffffffu, node);      // the entries served on my node
+    const int cnt = __popc(peers);
+    const bool leader = is_remote && (__ffs(peers) - 1) == lane;     // first touch of a remote node
+    const unsigned leaders = __ballot_sync(0xffffffffu, leader);
+    const int ng = __popc(leaders);
+    __syncwarp();
+    if (leader) grp_node[__popc(leaders & ((1u << lane) - 1u))] = node;
+    __syncwarp();
+    unsigned tried = 0;
+    bool moved = false;
+    for (int round = 0; round < ng && !moved; ++round) {
+      // least-touched remote node first, ties by node id
+      const unsigned key = (leader && !((tried >> lane) & 1u)) ? ((unsigned)cnt << 16 | (unsigned)node) : 0xffffffffu;
+      const unsigned best_key = __reduce_min_sync(0xffffffffu, key);
+      const int best_lane = __ffs(__ballot_sync(0xffffffffu, key == best_key)) - 1;
+      tried |= 1u << best_lane;
+      const int n = (int)(best_key & 0xffffu);
+      const int best_q = __popc(leaders & ((1u << best_lane) - 1u));
+      const bool in = is_remote && node == n;
+      bool ok = true;
+      int jo = -1, jt = -1;
+      if (in) {
+        const int c = v.cc[g];
+        const int base = g * CM;
+        for (int jj = 0; jj < c; ++jj) {
+          const int rp = v.pk ? (v.pk[base + jj] & 0xffffff) : v.rphys[base + jj];
+          if (rp == ph) { jo = jj; break; }
+        }
+        if (jo < 0 || budget(v.rel + base + jo) <= 0) ok = false;
+        // targets: home, then the other touched nodes in first-touch order
+        for (int ti = -1; ok && ti < ng && jt < 0; ++ti) {
+          if (ti == best_q) continue;
+          const int m = ti < 0 ? home : grp_node[ti];
+          for (int jj = 0; jj < c; ++jj) {
+            const int rr = v.pk ? (v.pk[base + jj] >> 24) : v.rep[base + jj];
+            if (rr / L == m && budget(v.ext + base + jj) > 0) { jt = jj; break; }
+          }
+        }
+        if (jt < 0) ok = false;
+      }
+      if (__any_sync(0xffffffffu, in && !ok)) continue;       // all or nothing per node
+      if (dry) return 1;
+      if (in) {
+        const int base = g * CM;
+        atomicSub(&v.rel[base + jo], 1);
+        atomicAdd(&v.ext[base + jo], 1);
+        atomicSub(&v.ext[base + jt], 1);
+        atomicAdd(&v.rel[base + jt], 1);
+        ph = v.pk ? (v.pk[base + jt] & 0xffffff) : v.rphys[base + jt];
+        node = (v.pk ? (v.pk[base + jt] >> 24) : v.rep[base + jt]) / L;
+      }
+      moves += __popc(__ballot_sync(0xffffffffu, in));
+      moved = true;
+      __syncwarp();
+    }
+    if (!moved) break;
+  }
+  if (!dry && moves > 0 && active) row_ph[lane] = ph;
+  return dry ? 0 : moves;
+}
+
+__global__ void __launch_bounds__(kVacWarps * 32) route_vacate_kernel(FinishArgs a, int staged, int chunk) {
+  if (blockIdx.x != 0) return;
+  const int R = a.R, L = a.L, K = a.K, nlp = a.nlp, G = a.G;
+  if (K > 32) {                 // more entries per token than lanes
+    if (threadIdx.x == 0) vacate_serial(a);
+    return;
+  }
+  extern __shared__ int vac_sm[];
+  __shared__ int grp_node_s[kVacWarps][32];
+  __shared__ int can_move_s[kVacWarps];
+  __shared__ int moves_s;
+  const int CM = route_cm(R);
+  const RouteWs w = route_ws_layout(G, R);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int GC = G * CM;
+  VacateTabs v{};
+  v.rel = a.ws + w.rel; v.ext = a.ws + w.ext; v.pk = nullptr;
+  v.rep = a.ws + w.rep; v.rphys = a.ws + w.rphys; v.cc = a.ws + w.c;
+  v.CM = CM; v.L = L; v.nlp = nlp; v.home = a.my_rank / L; v.K = K;
+  int* tok = vac_sm;
+  if (tid == 0) moves_s = 0;
+  if (staged) {
+    int* rel = vac_sm;
+    int* ext = vac_sm + GC;
+    int* pk = vac_sm + 2 * GC;
+    int* cs = vac_sm + 3 * GC;
+    tok = cs + G;
+    for (int i = tid; i < GC; i += blockDim.x) {
+      rel[i] = a.ws[w.rel + i];
+      ext[i] = a.ws[w.ext + i];
+      pk[i] = (v.rphys[i] & 0xffffff) | (v.rep[i] << 24);
+    }
+    for (int i = tid; i < G; i += blockDim.x) cs[i] = v.cc[i];
+    v.rel = rel; v.ext = ext; v.pk = pk; v.cc = cs;
+  }
+  int* tok_ph = tok;
+  int* tok_tk = tok + chunk * K;
+  int moves = 0;
+  for (int s0 = 0; s0 < a.S; s0 += chunk) {
+    const int ns = min(chunk, a.S - s0);
+    __syncthreads();
+    for (int i = tid; i < ns * K; i += blockDim.x) {
+      tok_ph[i] = a.phys_own[(size_t)s0 * K + i];
+      tok_tk[i] = a.topk_own[(size_t)s0 * K + i];
+    }
+    __syncthreads();
+    int t = 0;
+    while (t < ns) {
+      const int mine = t + warp;
+      int can = 0;
+      if (mine < ns) can = vacate_token(v, tok_ph + mine * K, tok_tk + mine * K, grp_node_s[warp], true);
+      if (lane == 0) can_move_s[warp] = can;
+      __syncthreads();
+      int first = kVacWarps;
+      for (int q = kVacWarps - 1; q >= 0; --q)
+        if (can_move_s[q]) first = q;
+      if (first < kVacWarps) {
+        if (warp == first) moves += vacate_token(v, tok_ph + mine * K, tok_tk + mine * K, grp_node_s[warp], false);
+        t += first + 1;
+      } else {
+        t += kVacWarps;
+      }
+      __syncthreads();
+    }
+    for (int i = tid; i < ns * K; i += blockDim.x) a.phys_own[(size_t)s0 * K + i] = tok_ph[i];
+  }
+  if (lane == 0 && moves) atomicAdd(&moves_s, moves);
+  __syncthreads();
+  if (staged)
+    for (int i = tid; i < GC; i += blockDim.x) {
+      a.ws[w.rel + i] = v.rel[i];
+      a.ws[w.ext + i] = v.ext[i];
+    }
+  if (tid == 0 && a.stats) a.stats[1] = moves_s;
 }
 
 __global__ void route_finish_kernel(FinishArgs a) {

@@ -644,6 +644,13 @@ static std::mutex g_attr_mutex;
 static size_t g_pass2_granted[kMaxDevices] = {};
 static bool g_swap_attr[kMaxDevices] = {};
 
+// ZEPP_B200_VACATE_STAGED=0 keeps the vacate pass's budget tables in global memory even when they would fit in
+// shared memory (the form large expert counts take), so that tests reach it on small cases.
+static bool vacate_tables_in_global() {
+  const char* e = getenv("ZEPP_B200_VACATE_STAGED");
+  return e != nullptr && e[0] == '0';
+}
+
 static int pass2_prepare(size_t bytes) {
   if (bytes > 200 * 1024) return fail("metadata: %zu bytes of shared memory per tile exceed the SM", bytes);
   if (bytes <= 48 * 1024) return 0;
@@ -747,7 +754,8 @@ extern "C" int zepp_layer_prepare_phase(zepp_layer* l, int phase, const int32_t*
       fa.world = R; fa.epoch_ptr = l->step_ctr; fa.block_counter = l->counters + 0; fa.status = l->status;
       fa.stats = l->route_stats;
       if (l->NN > 1) {
-        route_vacate_kernel<<<1, 32, 0, st>>>(fa);
+        const VacateShape vs = vacate_shape(l->G, R, l->K, l->nlp, vacate_tables_in_global());
+        route_vacate_kernel<<<1, kVacWarps * 32, vs.smem, st>>>(fa, vs.staged, vs.chunk);
         LAUNCH_OK();
       }
       route_finish_kernel<<<8, 256, 0, st>>>(fa);
@@ -1153,7 +1161,8 @@ extern "C" int zepp_route(const int32_t* topk_own, int S, int K, const int32_t* 
   fa.L = L; fa.nlp = nlp; fa.my_rank = my_rank; fa.ws = ws; fa.send_row = send_row; fa.world = 0; fa.epoch_ptr = nullptr;
   fa.status = nullptr; fa.stats = (long long*)stats;
   if (R / L > 1 && topk_own != nullptr) {
-    route_vacate_kernel<<<1, 32, 0, st>>>(fa);
+    const VacateShape vs = vacate_shape(G, R, K, nlp, vacate_tables_in_global());
+    route_vacate_kernel<<<1, kVacWarps * 32, vs.smem, st>>>(fa, vs.staged, vs.chunk);
     CU_OK(cudaGetLastError());
   }
   if (send_row != nullptr && probs_own != nullptr) {
