@@ -39,12 +39,30 @@ def test_layer_across_gpus(strategy):
     assert r.stdout.count("PASS") == nproc, r.stdout[-3000:]
 
 
+def _moves(stdout):
+    """Total moves (prime + steps) rank 0 reports."""
+    for line in stdout.splitlines():
+        if "rank 0/" in line and "moves (prime + steps)" in line:
+            return int(line.rsplit(" ", 1)[1])
+    return -1
+
+
 def test_layer_across_gpus_with_swap():
-    """Expert swap across real GPUs: moved experts' weights are pulled over NVLink from the source rank's slots."""
+    """Expert swap across real GPUs: moved experts' weights are pulled over NVLink from the source rank's slots
+    by the GEMM kernels, in the priming pass and in graph-replayed steps; decisions and outputs against the oracle
+    on every step.  The routings are chosen (by running the oracle's decision on them) so that experts do move at
+    the rank count of the run: a balanced two-rank layer only swaps under a strongly skewed, drifting popularity."""
     n = torch.cuda.device_count()
     if n < 2:
         pytest.skip("needs at least two GPUs")
     nproc = 2 if n < 4 else (4 if n < 8 else 8)
-    r = _run(nproc, "--strategy", "overlap", "--swap", "1", "--steps", "4")
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
-    assert r.stdout.count("PASS") == nproc, r.stdout[-3000:]
+    if nproc == 2:
+        runs = [("--zipf", "3.0", "--drift", "1.0"),                              # moves in replayed steps
+                ("--zipf", "3.0", "--drift", "1.0", "--prime-seed", "1004")]      # moves in the priming pass
+    else:
+        runs = [("--zipf", "1.2", "--drift", "0.5", "--prime-seed", "1004")]      # both
+    for extra in runs:
+        r = _run(nproc, "--strategy", "overlap", "--swap", "1", "--steps", "4", *extra)
+        assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+        assert r.stdout.count("PASS") == nproc, r.stdout[-3000:]
+        assert _moves(r.stdout) > 0, "no expert moved: " + r.stdout[-1500:]

@@ -157,8 +157,12 @@ class EPMoE(torch.nn.Module):
 
     # -- setup ------------------------------------------------------------------------
     def prime(self, topk_ids, topk_weights):
-        """One planning pass with every rank quiesced (loads kernels, checks the routing)."""
+        """One planning pass with every rank quiesced (loads kernels, checks the routing).  With swap on the pass
+        is a whole step on zero tokens: the swap decision is part of planning, and the experts it moves travel
+        inside the GEMM kernels of the same step, so a plan is always followed by its forward."""
         plan = self.prepare(topk_ids, topk_weights)
+        if self.cfg.swap:
+            self.forward(torch.zeros(self._tokens, self.cfg.shape.hidden, dtype=self.dtype, device=self.device), plan)
         self.check()
         self._barrier()
         return plan
@@ -210,6 +214,8 @@ class EPMoE(torch.nn.Module):
 
     def prepare(self, topk_ids, topk_weights, marks=None, phase=None):
         """Loads exchange -> (swap decision) -> route -> routing exchange -> metadata; returns the Plan.
+        With swap on, run forward() on this plan before the next prepare(): the weights of the experts a decision
+        moves are pulled by the forward's GEMM kernels.
         `phase` (0..3) runs one stage only: ranks emulated inside one process advance in lock step.
         The id / weight tensors are read in place by the step's kernels (keep them unchanged until then)."""
         ids, wts = self._ids(topk_ids, topk_weights)
